@@ -1,0 +1,124 @@
+/*
+ * smoltts_b200 -- C ABI of the hybrid language-model engine (libsmoltts_b200_lm.so): decoder-only models whose layers
+ * mix tokens either by softmax attention over a paged key/value pool or by a recurrent matrix state kept in per-sequence
+ * slots.  Same conventions as smoltts_b200.h: plain C types, every pointer is a DEVICE pointer owned by the caller unless
+ * said otherwise, every compute call is asynchronous on the given cudaStream_t (passed as void*), no allocation after
+ * create, 0 / negative SMOL_ERR_* return codes with smol_lm_last_error().
+ *
+ * One step runs a ragged batch: any number of sequences, each bringing its next tokens (a portion of a prompt or one
+ * decoded token), against the pages and the state slot the caller's scheduler gave it.
+ *
+ * Element type: `dtype` 0 = bfloat16 matrices, GEMM inputs and key/value pool (fp32 accumulation), 1 = float32
+ * everywhere (plain FMA arithmetic, no reduced-precision matrix mode).  In both, the residual stream, every norm, the
+ * attention scores and weights, and everything inside the recurrence are fp32.
+ */
+#ifndef SMOLTTS_B200_LM_H
+#define SMOLTTS_B200_LM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMOL_LM_ABI_VERSION 1
+
+enum { SMOL_LM_BF16 = 0, SMOL_LM_F32 = 1 };
+/* token mixers */
+enum { SMOL_LM_MIX_SINK_ATTENTION = 0, SMOL_LM_MIX_GENERAL_DELTA = 1 };
+/* feed-forward kinds */
+enum { SMOL_LM_MLP_NONE = 0, SMOL_LM_MLP_POLYNORM = 1 };
+
+/* One layer: sizes, constants and weights.  Matrices (`const void*`) have the engine's element type and are [out, in]
+ * row-major; vectors (`const float*`) are always fp32. */
+typedef struct SmolLmLayer {
+    int32_t mixer;            /* SMOL_LM_MIX_* */
+    int32_t heads, kv_heads;  /* query heads; key/value heads (recurrent mixer: = heads) */
+    int32_t dim, vdim;        /* per-head key size and value size (recurrent mixer: vdim = dim) */
+    int32_t rank;             /* recurrent mixer: inner size of the low-rank decay projection */
+    int32_t mlp, ff;          /* SMOL_LM_MLP_*, feed-forward size */
+    float score_scale;        /* attention: multiplies q.k */
+    float decay_coef;         /* recurrent: decay = exp(-decay_coef * sigmoid(.)) */
+    float unit_eps;           /* recurrent: unit key = k / sqrt(sum k^2 + unit_eps) */
+    /* fused input projection [n_in, width]; attention rows: q | k | v | gate; recurrent rows: r | k | v | gate | rate | decay-inner */
+    const void* w_in;
+    const void* w_out;        /* [width, heads * vdim] */
+    const void* w_up;         /* [ff, width] */
+    const void* w_down;       /* [width, ff] */
+    const float *norm1, *norm1b, *norm2, *norm2b;   /* one-plus RMS-norm weights [width] (pre / post of each sublayer) */
+    const float *ls1, *ls2;                         /* layer scales [width] */
+    const float *q_norm, *k_norm;                   /* attention: plain RMS-norm weights [dim] */
+    const float *dist_r1, *dist_r2, *sink;          /* attention: distance penalty r1 ln(1 + r2 (i - j)) and sink logit, [heads] */
+    const float *rate_bias;                         /* recurrent: [heads * dim] */
+    const float *decay_w2, *decay_bias;             /* recurrent: [heads * dim, rank] fp32, [heads * dim] */
+    const float *out_norm;                          /* recurrent: plain weight after the per-head RMS division [heads * dim] */
+    const float *act;                               /* PolyNorm coefficients a, b, c, e */
+} SmolLmLayer;
+
+typedef struct SmolLmConfig {
+    int32_t dtype;            /* SMOL_LM_BF16 / SMOL_LM_F32 */
+    int32_t vocab, width;
+    int32_t n_layers;         /* entries of the layer array */
+    int32_t n_runs;           /* layer runs per token: a looped layer counts once per pass; each run owns its cache or state */
+    int32_t page_size;        /* positions per key/value page */
+    int32_t max_step_tokens;  /* rows of the workspace: most tokens one step may bring */
+    int32_t max_step_seqs;    /* most sequences in one step */
+    int32_t max_want;         /* most logits rows asked for in one step */
+    float embed_scale, norm_eps;
+} SmolLmConfig;
+
+typedef struct SmolLmGlobals {
+    const void* embed;        /* [vocab, width] */
+    const void* head;         /* [vocab, width] */
+    const float* final_norm;  /* [width] one-plus weight */
+} SmolLmGlobals;
+
+/* A ragged batch.  All arrays live on the device. */
+typedef struct SmolLmStep {
+    int32_t n_tokens, n_seqs, n_want, max_pages;
+    const int32_t* tokens;       /* [n_tokens] ids, sequences one after the other */
+    const int32_t* tok_seq;      /* [n_tokens] index of the token's sequence in this step */
+    const int32_t* tok_pos;      /* [n_tokens] position in its sequence, counted from 0 */
+    const int32_t* seq_start;    /* [n_seqs + 1] first row of each sequence */
+    const int32_t* seq_pos0;     /* [n_seqs] positions the sequence already holds (0: a new sequence, state starts at zero) */
+    const int32_t* seq_slot;     /* [n_seqs] state slot */
+    const int32_t* block_table;  /* [n_seqs][max_pages] pages of each sequence, in order */
+    const int32_t* want_rows;    /* [n_want] rows whose logits are wanted */
+    float* logits;               /* [n_want][vocab] */
+    float* trace;                /* NULL, or [n_runs][n_tokens][width]: the residual stream after every layer run */
+} SmolLmStep;
+
+typedef struct SmolLm SmolLm;
+
+int smol_lm_abi_version(void);
+const char* smol_lm_last_error(void);
+
+/* layers / run_layer are HOST arrays, copied.  run_layer[n] = index of the layer that run n executes. */
+int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers, const int32_t* run_layer, SmolLm** out);
+void smol_lm_destroy(SmolLm* m);
+
+size_t smol_lm_page_bytes(const SmolLm* m);       /* one page: page_size positions of every attention run's keys and values */
+size_t smol_lm_slot_bytes(const SmolLm* m);       /* one slot: the fp32 matrix states of every recurrent run */
+size_t smol_lm_workspace_bytes(const SmolLm* m);
+
+int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace, size_t workspace_bytes, void* d_pages, int32_t n_pages,
+                 void* d_slots, int32_t n_slots);
+
+int smol_lm_step(SmolLm* m, const SmolLmStep* s, void* stream);
+
+/* Sampling of `rows` logits rows with the library's integer-weight sampler (temperature / top-k / top-p / min-p, Philox
+ * counters seed, d_seq_id[row], d_step[row]); temp 0 = arg-max.  n <= 32768. */
+int smol_lm_sample(SmolLm* m, const float* d_logits, int32_t rows, int32_t n, float temp, int32_t top_k, float top_p, float min_p,
+                   uint64_t seed, const int32_t* d_seq_id, const int32_t* d_step, int32_t* d_out, void* stream);
+
+/* Stand-alone operations of the engine, for tests and benchmarks: y fp32 [M, N] = a [M, K] . w [N, K]^T in the engine's element type. */
+int smol_lm_linear(SmolLm* m, const void* d_a, const void* d_w, float* d_y, int32_t M, int32_t N, int32_t K, void* stream);
+
+int64_t smol_lm_launch_count(const SmolLm* m);
+int32_t* smol_lm_error_word(SmolLm* m);           /* device word, nonzero after a step that addressed outside its pools */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -15,12 +15,8 @@ SMOL_ABI_VERSION = 1
 SMOL_MAX_LAYERS = 64
 SMOL_MAX_FAST_LAYERS = 16
 
-SMOL_OK = 0
-SMOL_ERR_INVALID = -1
-SMOL_ERR_UNBOUND = -2
-SMOL_ERR_CUDA = -3
-SMOL_ERR_UNSUPPORTED = -4
-SMOL_ERR_CAPACITY = -5
+from ._errors import (SMOL_ERR_CAPACITY, SMOL_ERR_CUDA, SMOL_ERR_INVALID, SMOL_ERR_UNBOUND, SMOL_ERR_UNSUPPORTED, SMOL_OK,  # noqa: F401
+                      SmolError)
 
 
 class SmolConfig(C.Structure):
@@ -136,12 +132,6 @@ PROTOTYPES = {
 }
 
 _lib = None
-
-
-class SmolError(RuntimeError):
-    def __init__(self, code: int, message: str):
-        super().__init__(f"smoltts_b200 error {code}: {message}")
-        self.code = code
 
 
 def library_path() -> str:

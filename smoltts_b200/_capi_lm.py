@@ -1,0 +1,85 @@
+"""ctypes binding of ``include/smoltts_b200_lm.h`` (hybrid language-model engine, ``libsmoltts_b200_lm.so``).
+
+Like ``_capi``: the library is built in-tree on first use when its sources changed, and loading never falls back to
+another implementation.  Struct layouts mirror the header field by field.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+from ._errors import SMOL_OK, SmolError
+
+SMOL_LM_ABI_VERSION = 1
+SMOL_LM_BF16, SMOL_LM_F32 = 0, 1
+
+
+class SmolLmLayer(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rank", "mlp", "ff")] + [
+        (n, C.c_float) for n in ("score_scale", "decay_coef", "unit_eps")] + [
+        (n, C.c_void_p) for n in ("w_in", "w_out", "w_up", "w_down", "norm1", "norm1b", "norm2", "norm2b", "ls1", "ls2",
+                                  "q_norm", "k_norm", "dist_r1", "dist_r2", "sink", "rate_bias", "decay_w2", "decay_bias",
+                                  "out_norm", "act")]
+
+
+class SmolLmConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
+                                         "max_step_seqs", "max_want")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
+
+
+class SmolLmGlobals(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("embed", "head", "final_norm")]
+
+
+class SmolLmStep(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "n_seqs", "n_want", "max_pages")] + [
+        (n, C.c_void_p) for n in ("tokens", "tok_seq", "tok_pos", "seq_start", "seq_pos0", "seq_slot", "block_table", "want_rows",
+                                  "logits", "trace")]
+
+
+PROTOTYPES = {
+    "smol_lm_abi_version": (C.c_int, []),
+    "smol_lm_last_error": (C.c_char_p, []),
+    "smol_lm_create": (C.c_int, [C.POINTER(SmolLmConfig), C.POINTER(SmolLmLayer), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)]),
+    "smol_lm_destroy": (None, [C.c_void_p]),
+    "smol_lm_page_bytes": (C.c_size_t, [C.c_void_p]),
+    "smol_lm_slot_bytes": (C.c_size_t, [C.c_void_p]),
+    "smol_lm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
+    "smol_lm_bind": (C.c_int, [C.c_void_p, C.POINTER(SmolLmGlobals), C.c_void_p, C.c_size_t, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]),
+    "smol_lm_step": (C.c_int, [C.c_void_p, C.POINTER(SmolLmStep), C.c_void_p]),
+    "smol_lm_sample": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_float, C.c_float, C.c_uint64,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "smol_lm_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "smol_lm_launch_count": (C.c_int64, [C.c_void_p]),
+    "smol_lm_error_word": (C.c_void_p, [C.c_void_p]),
+}
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LM_LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Loads (building first if necessary) the language-model library.  Raises if it cannot."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = os.environ.get("SMOLTTS_B200_LM_LIB") or _build.build(target="lm")
+    lib = C.CDLL(path)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if lib.smol_lm_abi_version() != SMOL_LM_ABI_VERSION:
+        raise RuntimeError(f"{path}: ABI version {lib.smol_lm_abi_version()} != {SMOL_LM_ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != SMOL_OK:
+        msg = load().smol_lm_last_error()
+        raise SmolError(rc, msg.decode() if msg else "")

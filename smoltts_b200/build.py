@@ -1,7 +1,8 @@
-"""In-tree build of the C-ABI library (nvcc, sm_100a only).
+"""In-tree build of the C-ABI libraries (nvcc, sm_100a only).
 
-``python -m smoltts_b200.build`` compiles ``csrc/*.cu`` into
-``smoltts_b200/_lib/libsmoltts_b200.so``.  nvcc cross-compiles without a GPU, so this
+``python -m smoltts_b200.build`` compiles ``csrc/*.cu`` into ``smoltts_b200/_lib/``: ``libsmoltts_b200.so`` (DualAR decode
+engine + Mimi decoder, target ``"core"``) and ``libsmoltts_b200_lm.so`` (hybrid language-model engine, target ``"lm"``).
+A model loads -- and, when sources changed, builds -- only the library it runs on.  nvcc cross-compiles without a GPU, so this
 also runs in the CPU-only build container; the .so is git-ignored but travels to the
 GPU box with the repo snapshot.
 """
@@ -21,6 +22,14 @@ STAMP = os.path.join(LIB_DIR, "build.stamp")
 SOURCES = ["decode_kernel.cu", "ll2_kernel.cu", "capi.cu", "mimi_kernels.cu"]
 HEADERS = ["common.cuh", "dev_model.h", "sampler.cuh", "umma.cuh", "tc_phases.cuh", "tmap_host.h", os.path.join("..", "..", "include", "smoltts_b200.h"),
            os.path.join("..", "..", "include", "smoltts_b200_mimi.h")]
+LM_LIB_PATH = os.path.join(LIB_DIR, "libsmoltts_b200_lm.so")
+# target -> (library, stamp, sources, headers)
+TARGETS = {
+    "core": (LIB_PATH, STAMP, SOURCES, HEADERS),
+    "lm": (LM_LIB_PATH, os.path.join(LIB_DIR, "build_lm.stamp"), ["lm_kernels.cu"],
+           ["common.cuh", "dev_model.h", "sampler.cuh", os.path.join("..", "..", "include", "smoltts_b200.h"),
+            os.path.join("..", "..", "include", "smoltts_b200_lm.h")]),
+}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -38,42 +47,49 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found (set NVCC=/path/to/nvcc)")
 
 
-def _digest() -> str:
+def _digest(target: str = "core") -> str:
+    _, _, sources, headers = TARGETS[target]
     h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
-    for name in SOURCES + HEADERS:
+    for name in sources + headers:
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(name.encode())
             h.update(f.read())
     return h.hexdigest()
 
 
-def is_current() -> bool:
-    if not (os.path.exists(LIB_PATH) and os.path.exists(STAMP)):
+def is_current(target: str = "core") -> bool:
+    lib, stamp = TARGETS[target][:2]
+    if not (os.path.exists(lib) and os.path.exists(stamp)):
         return False
-    with open(STAMP) as f:
-        return f.read().strip() == _digest()
+    with open(stamp) as f:
+        return f.read().strip() == _digest(target)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if sources changed; returns its path."""
-    if not force and is_current():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, target: str = "core") -> str:
+    """Compile one library if its sources changed; returns its path."""
+    lib, stamp, sources, _ = TARGETS[target]
+    if not force and is_current(target):
+        return lib
     os.makedirs(LIB_DIR, exist_ok=True)
     extra = os.environ.get("SMOL_EXTRA_NVCC", "").split()
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *[os.path.join(CSRC, s) for s in SOURCES], "-o", LIB_PATH, "-lcudart"]
+    tmp = f"{lib}.{os.getpid()}.tmp"          # concurrent first calls must never load a half-written library
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *[os.path.join(CSRC, s) for s in sources], "-o", tmp, "-lcudart"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     log = proc.stdout + proc.stderr
-    with open(os.path.join(LIB_DIR, "build.log"), "w") as f:
+    with open(os.path.join(LIB_DIR, f"build_{target}.log"), "w") as f:
         f.write(" ".join(cmd) + "\n" + log)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{log[-6000:]}")
+    os.replace(tmp, lib)
     if verbose:
         print(log)
-    with open(STAMP, "w") as f:
-        f.write(_digest())
-    return LIB_PATH
+    with open(stamp, "w") as f:
+        f.write(_digest(target))
+    return lib
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print(path)
+    for tgt in TARGETS:
+        if "--only" in sys.argv and sys.argv[sys.argv.index("--only") + 1] != tgt:
+            continue
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, target=tgt))

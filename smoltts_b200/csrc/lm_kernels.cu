@@ -1,0 +1,890 @@
+// Hybrid language-model engine (sm_100a): ragged-batch step over a paged key/value pool and per-sequence recurrent
+// state slots.  See include/smoltts_b200_lm.h for the contract of every entry point.
+//
+// Precision: the residual stream, all norms, attention scores / softmax weights and the whole recurrence run in fp32.
+// T (bf16 or float) is the element type of matrices, of the inputs of the matrix products and of the key/value pool;
+// every matrix product accumulates in fp32 and writes fp32.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/smoltts_b200_lm.h"
+#include "common.cuh"
+#include "sampler.cuh"
+
+#define SMOL_OK 0
+#define SMOL_ERR_INVALID (-1)
+#define SMOL_ERR_UNBOUND (-2)
+#define SMOL_ERR_CUDA (-3)
+#define SMOL_ERR_UNSUPPORTED (-4)
+#define SMOL_ERR_CAPACITY (-5)
+
+namespace smol {
+namespace lm {
+
+template <class T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <class T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// Sum over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        float t = l < nw ? red[l] : 0.0f;
+        t = warp_sum(t);
+        if (l == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Embedding: x[t] = embed[token[t]] * scale, then the first layer's norm (one-plus weight) -> hn.
+template <class T>
+__global__ void embed_norm_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ embed, float scale, int D, int vocab,
+                                  const float* __restrict__ wn, float eps, float* __restrict__ x, T* __restrict__ hn) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const T* e = embed + (size_t)tok * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = to_f<T>(e[c]) * scale;
+        x[(size_t)t * D + c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[(size_t)t * D + c] = from_f<T>(x[(size_t)t * D + c] * r * (1.0f + wn[c]));
+}
+
+// RMS norm of selected rows (one-plus weight) -> T.  rows == nullptr: row r of the output is row r of the input.
+template <class T>
+__global__ void norm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w, float eps,
+                                 int D, T* __restrict__ out) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) ss += xr[c] * xr[c];
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) out[(size_t)r * D + c] = from_f<T>(xr[c] * s * (1.0f + w[c]));
+}
+
+// End of a sublayer fused with the start of the next one:
+//   x <- x + ls * (y / rms(y) * (1 + wb));   hn <- x / rms(x) * (1 + wn)     (wn == nullptr: no next norm)
+// One block per row; the new row is kept in shared memory between the two passes.
+template <class T>
+__global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
+                                const float* __restrict__ ls, const float* __restrict__ wn, float eps, int D, T* __restrict__ hn) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const size_t o = (size_t)blockIdx.x * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y[o + c]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+    float s2 = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = x[o + c] + ls[c] * (y[o + c] * r * (1.0f + wb[c]));
+        x[o + c] = v;
+        row[c] = v;
+        s2 += v * v;
+    }
+    if (!wn) return;
+    s2 = block_sum(s2, red);
+    const float r2 = 1.0f / sqrtf(s2 / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[o + c] = from_f<T>(row[c] * r2 * (1.0f + wn[c]));
+}
+
+// PolyNorm: out = a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e over a token's feed-forward vector.
+template <class T>
+__global__ void polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, float eps, int F, T* __restrict__ out) {
+    __shared__ float red[33];
+    const size_t o = (size_t)blockIdx.x * F;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+        const float v = z[o + c], v2 = v * v;
+        s2 += v2;
+        s4 += v2 * v2;
+        s6 += v2 * v2 * v2;
+    }
+    s2 = block_sum(s2, red);
+    s4 = block_sum(s4, red);
+    s6 = block_sum(s6, red);
+    const float a = coef[0] / sqrtf(s2 / (float)F + eps), b = coef[1] / sqrtf(s4 / (float)F + eps),
+                cc = coef[2] / sqrtf(s6 / (float)F + eps), e = coef[3];
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+        const float v = z[o + c];
+        out[o + c] = from_f<T>(a * v + b * v * v + cc * v * v * v + e);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Matrix product, fp32: y[M, N] = a[M, K] . w[N, K]^T with plain FMAs, k ascending (the result of a row does not depend on M).
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ w,
+                                                                        float* __restrict__ y, int M, int N, int K) {
+    constexpr int NT = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 1];
+    __shared__ float Ws[BK][BN + 1];
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += NT) {
+            const int r = i / BK, c = i % BK;
+            As[c][r] = (m0 + r < M && k0 + c < K) ? a[(size_t)(m0 + r) * K + k0 + c] : 0.0f;
+        }
+        for (int i = threadIdx.x; i < BN * BK; i += NT) {
+            const int r = i / BK, c = i % BK;
+            Ws[c][r] = (n0 + r < N && k0 + c < K) ? w[(size_t)(n0 + r) * K + k0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float av[TM], wv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) wv[j] = Ws[k][tx + j * (BN / TN)];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int m = m0 + ty * TM + i, n = n0 + tx + j * (BN / TN);
+            if (m < M && n < N) y[(size_t)m * N + n] = acc[i][j];
+        }
+}
+
+// Matrix product, bf16 inputs on the tensor cores (mma.sync m16n8k16, fp32 accumulation): 4 warps, tile (WR*MT*16) x (WC*NT*8),
+// K in steps of 32 through shared memory, the next step's global loads in flight during the MMAs.
+constexpr int kGemmBK = 32;
+constexpr int kGemmLd = kGemmBK + 8;   // 80-byte rows: fragment loads hit 32 distinct banks
+
+template <int ROWS>
+__device__ __forceinline__ void gemm_fetch(const bf16* __restrict__ src, int r0, int R, int K, int k0, bool vec, uint4 (&reg)[ROWS * 4 / 128]) {
+#pragma unroll
+    for (int i = 0; i < ROWS * 4 / 128; ++i) {
+        const int id = threadIdx.x + i * 128, r = id >> 2, c = (id & 3) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r0 + r < R) {
+            const bf16* p = src + (size_t)(r0 + r) * K + k0 + c;
+            if (vec && k0 + c + 8 <= K) {
+                v = *reinterpret_cast<const uint4*>(p);
+            } else {
+                uint16_t h[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = (k0 + c + e < K) ? reinterpret_cast<const uint16_t*>(p)[e] : (uint16_t)0;
+                v.x = h[0] | ((uint32_t)h[1] << 16); v.y = h[2] | ((uint32_t)h[3] << 16);
+                v.z = h[4] | ((uint32_t)h[5] << 16); v.w = h[6] | ((uint32_t)h[7] << 16);
+            }
+        }
+        reg[i] = v;
+    }
+}
+template <int ROWS>
+__device__ __forceinline__ void gemm_stash(bf16* dst, const uint4 (&reg)[ROWS * 4 / 128]) {
+#pragma unroll
+    for (int i = 0; i < ROWS * 4 / 128; ++i) {
+        const int id = threadIdx.x + i * 128, r = id >> 2, c = (id & 3) * 8;
+        *reinterpret_cast<uint4*>(dst + r * kGemmLd + c) = reg[i];
+    }
+}
+
+template <int WR, int WC, int MT, int NT>
+__global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ y,
+                                                        int M, int N, int K) {
+    static_assert(WR * WC == 4, "four warps");
+    constexpr int BM = WR * MT * 16, BN = WC * NT * 8;
+    static_assert(BM % 32 == 0 && BN % 32 == 0, "tile rows are fetched 32 at a time");
+    __shared__ __align__(16) bf16 As[2][BM * kGemmLd];
+    __shared__ __align__(16) bf16 Ws[2][BN * kGemmLd];
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int wm = (warp / WC) * MT * 16, wn = (warp % WC) * NT * 8;
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    uint4 ra[BM * 4 / 128], rw[BN * 4 / 128];
+    gemm_fetch<BM>(a, m0, M, K, 0, vec, ra);
+    gemm_fetch<BN>(w, n0, N, K, 0, vec, rw);
+    gemm_stash<BM>(As[0], ra);
+    gemm_stash<BN>(Ws[0], rw);
+    __syncthreads();
+    const int steps = (K + kGemmBK - 1) / kGemmBK;
+    for (int s = 0; s < steps; ++s) {
+        const int cur = s & 1;
+        if (s + 1 < steps) {
+            gemm_fetch<BM>(a, m0, M, K, (s + 1) * kGemmBK, vec, ra);
+            gemm_fetch<BN>(w, n0, N, K, (s + 1) * kGemmBK, vec, rw);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK; kk += 16) {
+            uint32_t af[MT][4], bfr[NT][2];
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                const bf16* p = As[cur] + (wm + i * 16 + g) * kGemmLd + kk + tq * 2;
+                af[i][0] = *reinterpret_cast<const uint32_t*>(p);
+                af[i][1] = *reinterpret_cast<const uint32_t*>(p + 8 * kGemmLd);
+                af[i][2] = *reinterpret_cast<const uint32_t*>(p + 8);
+                af[i][3] = *reinterpret_cast<const uint32_t*>(p + 8 * kGemmLd + 8);
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const bf16* p = Ws[cur] + (wn + j * 8 + g) * kGemmLd + kk + tq * 2;
+                bfr[j][0] = *reinterpret_cast<const uint32_t*>(p);
+                bfr[j][1] = *reinterpret_cast<const uint32_t*>(p + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_bf16_16816(acc[i][j], af[i][0], af[i][1], af[i][2], af[i][3], bfr[j][0], bfr[j][1]);
+        }
+        if (s + 1 < steps) {
+            gemm_stash<BM>(As[cur ^ 1], ra);
+            gemm_stash<BN>(Ws[cur ^ 1], rw);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int m = m0 + wm + i * 16 + g, n = n0 + wn + j * 8 + tq * 2;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int mm = m + (e >> 1) * 8, nn = n + (e & 1);
+                if (mm < M && nn < N) y[(size_t)mm * N + nn] = acc[i][j][e];
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention with a sink.  proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv].
+struct AttnArgs {
+    const float* proj;
+    int n_in;
+    const int32_t *tok_seq, *tok_pos, *block_table;
+    int max_pages, page_size, n_pages;
+    size_t page_elems, k_off, v_off;   // element offsets of this run's keys / values inside a page
+    int H, G, d, dv;
+    float scale, eps;
+    const float *q_norm, *k_norm, *r1, *r2, *sink;
+    int n_tokens;
+    int32_t* err;
+};
+
+// One warp per (token, slot): slots 0..H-1 norm a query head into qbuf, H..H+G-1 norm a key head into the pool,
+// H+G..H+2G-1 copy a value head into the pool.
+template <class T>
+__global__ void attn_prep_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __restrict__ pool) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int slots = A.H + 2 * A.G;
+    if (unit >= A.n_tokens * slots) return;
+    const int t = unit / slots, s = unit % slots;
+    const float* row = A.proj + (size_t)t * A.n_in;
+    if (s < A.H) {
+        const float* q = row + s * A.d;
+        float ss = 0.0f;
+        for (int c = lane; c < A.d; c += 32) ss += q[c] * q[c];
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)A.d + A.eps);
+        for (int c = lane; c < A.d; c += 32) qbuf[((size_t)t * A.H + s) * A.d + c] = from_f<T>(q[c] * r * A.q_norm[c]);
+        return;
+    }
+    const int pos = A.tok_pos[t];
+    const int pg = pos / A.page_size, in_pg = pos % A.page_size;
+    int page = pg < A.max_pages ? A.block_table[(size_t)A.tok_seq[t] * A.max_pages + pg] : -1;
+    if (page < 0 || page >= A.n_pages) {
+        if (lane == 0) atomicExch(A.err, 1);
+        return;
+    }
+    T* base = pool + (size_t)page * A.page_elems;
+    if (s < A.H + A.G) {
+        const int gk = s - A.H;
+        const float* k = row + A.H * A.d + gk * A.d;
+        float ss = 0.0f;
+        for (int c = lane; c < A.d; c += 32) ss += k[c] * k[c];
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)A.d + A.eps);
+        T* dst = base + A.k_off + ((size_t)gk * A.page_size + in_pg) * A.d;
+        for (int c = lane; c < A.d; c += 32) dst[c] = from_f<T>(k[c] * r * A.k_norm[c]);
+    } else {
+        const int gv = s - A.H - A.G;
+        const float* v = row + (A.H + A.G) * A.d + gv * A.dv;
+        T* dst = base + A.v_off + ((size_t)gv * A.page_size + in_pg) * A.dv;
+        for (int c = lane; c < A.dv; c += 32) dst[c] = from_f<T>(v[c]);
+    }
+}
+
+// One warp per (token, query head), 32 keys per round: lane j scores key j (full dot product, the query in shared
+// memory), the round's softmax weights are shared by shuffles and every lane accumulates dv / 32 output columns.
+// The sink enters as the initial state of the running softmax: maximum = sink, denominator = 1, no value.
+constexpr int kAttnWarps = 4;
+constexpr int kAttnMaxV = 8;   // value size up to 256
+
+template <class T>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool,
+                                                               T* __restrict__ out) {
+    extern __shared__ float qs_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * kAttnWarps + warp;
+    if (unit >= A.n_tokens * A.H) return;
+    const int t = unit / A.H, h = unit % A.H;
+    const int g = h / (A.H / A.G);
+    float* qs = qs_all + warp * A.d;
+    for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
+    __syncwarp();
+    const int pos = A.tok_pos[t];
+    const int32_t* bt = A.block_table + (size_t)A.tok_seq[t] * A.max_pages;
+    const float r1 = A.r1[h], r2 = A.r2[h];
+    float m = A.sink[h], l = 1.0f;
+    float o[kAttnMaxV];
+#pragma unroll
+    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+    for (int j0 = 0; j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        float s = -INFINITY;
+        const T* vrow = nullptr;
+        if (j <= pos) {
+            const int page = bt[j / A.page_size], in_pg = j % A.page_size;
+            const T* base = pool + (size_t)page * A.page_elems;
+            const T* k = base + A.k_off + ((size_t)g * A.page_size + in_pg) * A.d;
+            vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv;
+            float dot = 0.0f;
+            for (int c = 0; c < A.d; ++c) dot = fmaf(qs[c], to_f<T>(k[c]), dot);
+            s = dot * A.scale - r1 * log1pf(r2 * (float)(pos - j));
+        }
+        const float mn = fmaxf(m, warp_max(s));
+        const float p = (j <= pos) ? expf(s - mn) : 0.0f;
+        const float corr = expf(m - mn);
+        l = l * corr + warp_sum(p);
+        m = mn;
+#pragma unroll
+        for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
+        const int cnt = min(32, pos - j0 + 1);
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const T* vr = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(vrow), jj));
+#pragma unroll
+            for (int e = 0; e < kAttnMaxV; ++e) {
+                const int c = lane + e * 32;
+                if (c < A.dv) o[e] = fmaf(pj, to_f<T>(vr[c]), o[e]);
+            }
+        }
+    }
+    const float inv = 1.0f / l;
+    const float* gate = A.proj + (size_t)t * A.n_in + A.H * A.d + A.G * A.d + A.G * A.dv + h * A.dv;
+#pragma unroll
+    for (int e = 0; e < kAttnMaxV; ++e) {
+        const int c = lane + e * 32;
+        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * sigmoidf_(gate[c]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Generalized delta rule.  proj row layout: r | k | v | gate | rate (each H*d), then the decay's inner vector [rank].
+struct DeltaArgs {
+    const float* proj;
+    int n_in, H, d, rank, n_tokens;
+    float decay_coef, unit_eps, eps;
+    const float *rate_bias, *decay_w2, *decay_bias, *out_norm;
+    const int32_t *seq_start, *seq_pos0, *seq_slot;
+    size_t slot_floats, state_off;
+    int n_slots;
+    int32_t* err;
+};
+
+// Per token and channel: decay w = exp(-coef * sigmoid(w2 tanh(inner) + bias)), unit key u, removal vector a * u.
+__global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, float* __restrict__ ukey, float* __restrict__ aukey) {
+    extern __shared__ float th[];   // tanh(inner) [rank], then per-head 1/|k|
+    const int t = blockIdx.x, HD = A.H * A.d;
+    const float* row = A.proj + (size_t)t * A.n_in;
+    float* inv = th + A.rank;
+    for (int r = threadIdx.x; r < A.rank; r += blockDim.x) th[r] = tanhf(row[5 * HD + r]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int h = warp; h < A.H; h += nw) {
+        const float* k = row + HD + h * A.d;
+        float ss = 0.0f;
+        for (int c = lane; c < A.d; c += 32) ss += k[c] * k[c];
+        ss = warp_sum(ss);
+        if (lane == 0) inv[h] = 1.0f / sqrtf(ss + A.unit_eps);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+        float lo = A.decay_bias[c];
+        const float* w2 = A.decay_w2 + (size_t)c * A.rank;
+        for (int r = 0; r < A.rank; ++r) lo = fmaf(w2[r], th[r], lo);
+        const float u = row[HD + c] * inv[c / A.d];
+        const float a = sigmoidf_(row[4 * HD + c] + A.rate_bias[c]);
+        decay[(size_t)t * HD + c] = expf(-A.decay_coef * sigmoidf_(lo));
+        ukey[(size_t)t * HD + c] = u;
+        aukey[(size_t)t * HD + c] = a * u;
+    }
+}
+
+// The recurrence.  One block per (sequence, head); thread j owns value column j of the state, S[i] = state[i][j] in
+// registers (DK >= d key channels; channels beyond d are padded with zero keys).  Tokens are staged through shared
+// memory kDeltaChunk at a time.  Per token:  seen = sum_i u_i S_i;  S_i <- w_i S_i - (a u)_i seen + k_i v_j;
+// o_j = sum_i S_i r_i.  The epilogue divides each head's o by its root mean square, applies the plain weight and the
+// sigmoid gate, and writes the mixer's output in T.
+constexpr int kDeltaChunk = 8;
+
+template <int DK, class T>
+__global__ void delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay, const float* __restrict__ ukey,
+                                  const float* __restrict__ aukey, float* __restrict__ state_pool, T* __restrict__ out) {
+    extern __shared__ float sh[];
+    const int d = A.d, HD = A.H * d;
+    float* s_r = sh;                             // [chunk][DK] each
+    float* s_k = s_r + kDeltaChunk * DK;
+    float* s_u = s_k + kDeltaChunk * DK;
+    float* s_au = s_u + kDeltaChunk * DK;
+    float* s_w = s_au + kDeltaChunk * DK;
+    float* s_red = s_w + kDeltaChunk * DK;       // [warps][chunk]
+    const int seq = blockIdx.x / A.H, h = blockIdx.x % A.H;
+    const int j = threadIdx.x;
+    const bool live = j < d;
+    const int nw = (blockDim.x + 31) >> 5, warp = j >> 5, lane = j & 31;
+    const int t0 = A.seq_start[seq], t1 = A.seq_start[seq + 1];
+    const int slot = A.seq_slot[seq];
+    if (slot < 0 || slot >= A.n_slots) {
+        if (j == 0) atomicExch(A.err, 2);
+        return;
+    }
+    float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * d;
+    float S[DK];
+    const bool fresh = A.seq_pos0[seq] == 0;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = (live && !fresh && i < d) ? st[(size_t)i * d + j] : 0.0f;
+    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
+        const int n = min(kDeltaChunk, t1 - c0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
+            const int tt = idx / DK, i = idx % DK;
+            const size_t prow = (size_t)(c0 + tt) * A.n_in, vrow = (size_t)(c0 + tt) * HD + h * d + i;
+            const bool in = i < d;
+            s_r[idx] = in ? A.proj[prow + h * d + i] : 0.0f;
+            s_k[idx] = in ? A.proj[prow + HD + h * d + i] : 0.0f;
+            s_u[idx] = in ? ukey[vrow] : 0.0f;
+            s_au[idx] = in ? aukey[vrow] : 0.0f;
+            s_w[idx] = in ? decay[vrow] : 0.0f;
+        }
+        __syncthreads();
+        float o[kDeltaChunk];
+#pragma unroll
+        for (int tt = 0; tt < kDeltaChunk; ++tt) {
+            o[tt] = 0.0f;
+            if (tt < n) {
+                const float v = live ? A.proj[(size_t)(c0 + tt) * A.n_in + 2 * HD + h * d + j] : 0.0f;
+                const float *pr = s_r + tt * DK, *pk = s_k + tt * DK, *pu = s_u + tt * DK, *pa = s_au + tt * DK, *pw = s_w + tt * DK;
+                float seen0 = 0.0f, seen1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DK; i += 2) {
+                    seen0 = fmaf(pu[i], S[i], seen0);
+                    seen1 = fmaf(pu[i + 1], S[i + 1], seen1);
+                }
+                const float seen = seen0 + seen1;
+                float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DK; i += 2) {
+                    S[i] = fmaf(pk[i], v, fmaf(pw[i], S[i], -pa[i] * seen));
+                    S[i + 1] = fmaf(pk[i + 1], v, fmaf(pw[i + 1], S[i + 1], -pa[i + 1] * seen));
+                    acc0 = fmaf(S[i], pr[i], acc0);
+                    acc1 = fmaf(S[i + 1], pr[i + 1], acc1);
+                }
+                o[tt] = acc0 + acc1;
+            }
+        }
+        // per-head mean of o^2 for every token of the chunk
+#pragma unroll
+        for (int tt = 0; tt < kDeltaChunk; ++tt) {
+            const float q = warp_sum(live ? o[tt] * o[tt] : 0.0f);
+            if (lane == 0) s_red[warp * kDeltaChunk + tt] = q;
+        }
+        __syncthreads();
+        if (live) {
+            const float nwgt = A.out_norm[h * d + j];
+#pragma unroll
+            for (int tt = 0; tt < kDeltaChunk; ++tt) {
+                if (tt < n) {
+                    float ss = 0.0f;
+                    for (int w = 0; w < nw; ++w) ss += s_red[w * kDeltaChunk + tt];
+                    const float gate = A.proj[(size_t)(c0 + tt) * A.n_in + 3 * HD + h * d + j];
+                    out[(size_t)(c0 + tt) * HD + h * d + j] =
+                        from_f<T>(o[tt] / sqrtf(ss / (float)d + A.eps) * nwgt * sigmoidf_(gate));
+                }
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DK; ++i)
+            if (i < d) st[(size_t)i * d + j] = S[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Sampling: the library's integer-weight sampler, one block per row.
+template <int PER>
+__global__ void __launch_bounds__(kThreads) lm_sample_kernel(const float* __restrict__ logits, int n, int rows, float temp, int top_k,
+                                                             float top_p, float min_p, unsigned long long seed,
+                                                             const int32_t* __restrict__ seq_id, const int32_t* __restrict__ step,
+                                                             int32_t* __restrict__ out) {
+    extern __shared__ __align__(16) float lg[];
+    __shared__ SampleScratch sc;
+    for (int b = blockIdx.x; b < rows; b += gridDim.x) {
+        for (int i = threadIdx.x; i < n; i += kThreads) lg[i] = logits[(size_t)b * n + i];
+        __syncthreads();
+        const int tok = sample_row<kThreads, PER>(lg, n, temp, top_k, top_p, min_p, seed, step ? (uint32_t)step[b] : 0u,
+                                                  seq_id ? (uint32_t)seq_id[b] : (uint32_t)b, 0u, sc);
+        if (threadIdx.x == 0) out[b] = tok;
+        __syncthreads();
+    }
+}
+
+}  // namespace lm
+}  // namespace smol
+
+// =====================================================================================================================
+// Host side
+using namespace smol::lm;
+using smol::bf16;
+
+static thread_local std::string g_err;
+static int fail(int code, const std::string& msg) {
+    g_err = msg;
+    return code;
+}
+#define CU(expr)                                                                                  \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess) return fail(SMOL_ERR_CUDA, std::string(#expr ": ") + cudaGetErrorString(e_)); \
+    } while (0)
+
+struct RunInfo {
+    int layer;
+    size_t k_off = 0, v_off = 0;   // attention: element offsets inside a page
+    size_t state_off = 0;          // recurrent: float offset inside a slot
+};
+
+struct SmolLm {
+    SmolLmConfig cfg;
+    std::vector<SmolLmLayer> layers;
+    std::vector<RunInfo> runs;
+    SmolLmGlobals g{};
+    size_t page_elems = 0, slot_floats = 0, esize = 2;
+    int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
+    // workspace carving (byte offsets)
+    size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_q, o_hw, o_err, total;
+    char* ws = nullptr;
+    void* pages = nullptr;
+    float* slots = nullptr;
+    int n_pages = 0, n_slots = 0;
+    bool bound = false;
+    int64_t launches = 0;
+};
+
+static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
+
+static int n_in_of(const SmolLmLayer& L) {
+    if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim + L.heads * L.vdim;
+    return 5 * L.heads * L.dim + L.rank;
+}
+
+extern "C" int smol_lm_abi_version(void) { return SMOL_LM_ABI_VERSION; }
+extern "C" const char* smol_lm_last_error(void) { return g_err.c_str(); }
+
+extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers, const int32_t* run_layer, SmolLm** out) {
+    if (!cfg || !layers || !run_layer || !out) return fail(SMOL_ERR_INVALID, "smol_lm_create: null argument");
+    if (cfg->dtype != SMOL_LM_BF16 && cfg->dtype != SMOL_LM_F32) return fail(SMOL_ERR_INVALID, "dtype must be 0 (bf16) or 1 (f32)");
+    if (cfg->vocab < 1 || cfg->width < 1 || cfg->n_layers < 1 || cfg->n_runs < 1 || cfg->page_size < 1 || cfg->max_step_tokens < 1 ||
+        cfg->max_step_seqs < 1 || cfg->max_want < 1)
+        return fail(SMOL_ERR_INVALID, "smol_lm_create: sizes must be positive");
+    SmolLm* m = new SmolLm();
+    m->cfg = *cfg;
+    m->esize = cfg->dtype == SMOL_LM_F32 ? 4 : 2;
+    m->layers.assign(layers, layers + cfg->n_layers);
+    for (int n = 0; n < cfg->n_runs; ++n) {
+        const int li = run_layer[n];
+        if (li < 0 || li >= cfg->n_layers) { delete m; return fail(SMOL_ERR_INVALID, "run_layer entry outside the layer array"); }
+        const SmolLmLayer& L = m->layers[li];
+        RunInfo r;
+        r.layer = li;
+        if (L.heads < 1 || L.dim < 1) { delete m; return fail(SMOL_ERR_INVALID, "a layer needs heads >= 1 and dim >= 1"); }
+        if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
+            if (L.kv_heads < 1 || L.heads % L.kv_heads != 0 || L.vdim < 1) { delete m; return fail(SMOL_ERR_INVALID, "attention: heads must be a multiple of kv_heads"); }
+            if (L.vdim > 32 * kAttnMaxV) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "attention: value size above 256"); }
+            r.k_off = m->page_elems;
+            r.v_off = r.k_off + (size_t)L.kv_heads * cfg->page_size * L.dim;
+            m->page_elems = r.v_off + (size_t)L.kv_heads * cfg->page_size * L.vdim;
+            m->max_q = std::max(m->max_q, L.heads * L.dim);
+            m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
+        } else if (L.mixer == SMOL_LM_MIX_GENERAL_DELTA) {
+            if (L.dim > 128) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 128"); }
+            if (L.rank < 1) { delete m; return fail(SMOL_ERR_INVALID, "recurrent mixer: rank must be positive"); }
+            r.state_off = m->slot_floats;
+            m->slot_floats += (size_t)L.heads * L.dim * L.dim;
+            m->max_hd = std::max(m->max_hd, L.heads * L.dim);
+            m->max_mix = std::max(m->max_mix, L.heads * L.dim);
+        } else {
+            delete m;
+            return fail(SMOL_ERR_UNSUPPORTED, "unknown mixer kind");
+        }
+        if (L.mlp != SMOL_LM_MLP_NONE && L.mlp != SMOL_LM_MLP_POLYNORM) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "unknown feed-forward kind"); }
+        if (L.mlp != SMOL_LM_MLP_NONE) m->max_ff = std::max(m->max_ff, L.ff);
+        m->max_in = std::max(m->max_in, n_in_of(L));
+        m->runs.push_back(r);
+    }
+    // pages hold 16-byte aligned rows whatever the sizes
+    m->page_elems = (m->page_elems + 7) / 8 * 8;
+    const size_t T = cfg->max_step_tokens, D = cfg->width, E = m->esize;
+    size_t o = 0;
+    auto carve = [&](size_t bytes) { size_t at = o; o += al256(bytes); return at; };
+    m->o_x = carve(T * D * 4);
+    m->o_hn = carve(T * D * E);
+    m->o_proj = carve(T * (size_t)m->max_in * 4);
+    m->o_mix = carve(T * (size_t)std::max(m->max_mix, 1) * E);
+    m->o_y = carve(T * D * 4);
+    m->o_z = carve(T * (size_t)std::max(m->max_ff, 1) * 4);
+    m->o_act = carve(T * (size_t)std::max(m->max_ff, 1) * E);
+    m->o_dec = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
+    m->o_u = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
+    m->o_au = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
+    m->o_q = carve(T * (size_t)std::max(m->max_q, 1) * E);
+    m->o_hw = carve((size_t)cfg->max_want * D * E);
+    m->o_err = carve(256);
+    m->total = o;
+    *out = m;
+    return SMOL_OK;
+}
+
+extern "C" void smol_lm_destroy(SmolLm* m) { delete m; }
+extern "C" size_t smol_lm_page_bytes(const SmolLm* m) { return m ? std::max<size_t>(m->page_elems, 8) * m->esize : 0; }
+extern "C" size_t smol_lm_slot_bytes(const SmolLm* m) { return m ? std::max<size_t>(m->slot_floats, 4) * 4 : 0; }
+extern "C" size_t smol_lm_workspace_bytes(const SmolLm* m) { return m ? m->total : 0; }
+extern "C" int64_t smol_lm_launch_count(const SmolLm* m) { return m ? m->launches : 0; }
+extern "C" int32_t* smol_lm_error_word(SmolLm* m) { return (m && m->bound) ? reinterpret_cast<int32_t*>(m->ws + m->o_err) : nullptr; }
+
+extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace, size_t workspace_bytes, void* d_pages, int32_t n_pages,
+                            void* d_slots, int32_t n_slots) {
+    if (!m || !g || !d_workspace || !d_pages || !d_slots) return fail(SMOL_ERR_INVALID, "smol_lm_bind: null argument");
+    if (workspace_bytes < m->total) return fail(SMOL_ERR_CAPACITY, "smol_lm_bind: workspace too small");
+    if (reinterpret_cast<uintptr_t>(d_workspace) % 256 || reinterpret_cast<uintptr_t>(d_pages) % 16)
+        return fail(SMOL_ERR_INVALID, "smol_lm_bind: workspace must be 256-byte aligned, pages 16-byte aligned");
+    if (n_pages < 1 || n_slots < 1) return fail(SMOL_ERR_INVALID, "smol_lm_bind: need at least one page and one slot");
+    if (!g->embed || !g->head || !g->final_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: missing global weights");
+    m->g = *g;
+    m->ws = static_cast<char*>(d_workspace);
+    m->pages = d_pages;
+    m->slots = static_cast<float*>(d_slots);
+    m->n_pages = n_pages;
+    m->n_slots = n_slots;
+    m->bound = true;
+    return SMOL_OK;
+}
+
+// y fp32 [M, N] = a [M, K] . w [N, K]^T
+template <class T>
+static cudaError_t linear(SmolLm* m, const T* a, const T* w, float* y, int M, int N, int K, cudaStream_t st);
+
+template <>
+cudaError_t linear<float>(SmolLm* m, const float* a, const float* w, float* y, int M, int N, int K, cudaStream_t st) {
+    if (M <= 16) {
+        dim3 grid((N + 63) / 64, (M + 15) / 16);
+        gemm_f32_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+    } else {
+        dim3 grid((N + 63) / 64, (M + 63) / 64);
+        gemm_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+    }
+    m->launches++;
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int M, int N, int K, cudaStream_t st) {
+    if (M <= 32) {
+        dim3 grid((N + 31) / 32, (M + 31) / 32);
+        gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 32 x 32
+    } else if (M <= 256) {
+        dim3 grid((N + 63) / 64, (M + 63) / 64);
+        gemm_bf16_kernel<2, 2, 2, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 64 x 64
+    } else {
+        dim3 grid((N + 63) / 64, (M + 127) / 128);
+        gemm_bf16_kernel<2, 2, 4, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 128 x 64
+    }
+    m->launches++;
+    return cudaGetLastError();
+}
+
+template <int DK, class T>
+static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec, const float* u, const float* au, float* pool, T* out,
+                               cudaStream_t st) {
+    const int threads = (A.d + 31) / 32 * 32;
+    const size_t smem = (size_t)(5 * kDeltaChunk * DK + 8 * kDeltaChunk) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    delta_scan_kernel<DK, T><<<n_seqs * A.H, threads, smem, st>>>(A, dec, u, au, pool, out);
+    return cudaGetLastError();
+}
+
+template <class T>
+static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
+    const SmolLmConfig& c = m->cfg;
+    const int Tn = s->n_tokens, D = c.width;
+    float* x = reinterpret_cast<float*>(m->ws + m->o_x);
+    T* hn = reinterpret_cast<T*>(m->ws + m->o_hn);
+    float* proj = reinterpret_cast<float*>(m->ws + m->o_proj);
+    T* mix = reinterpret_cast<T*>(m->ws + m->o_mix);
+    float* y = reinterpret_cast<float*>(m->ws + m->o_y);
+    float* z = reinterpret_cast<float*>(m->ws + m->o_z);
+    T* act = reinterpret_cast<T*>(m->ws + m->o_act);
+    float* dec = reinterpret_cast<float*>(m->ws + m->o_dec);
+    float* uk = reinterpret_cast<float*>(m->ws + m->o_u);
+    float* auk = reinterpret_cast<float*>(m->ws + m->o_au);
+    T* qbuf = reinterpret_cast<T*>(m->ws + m->o_q);
+    T* hw = reinterpret_cast<T*>(m->ws + m->o_hw);
+    int32_t* err = reinterpret_cast<int32_t*>(m->ws + m->o_err);
+    T* pool = static_cast<T*>(m->pages);
+    const int nthr = D >= 1024 ? 256 : 128;
+
+    embed_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
+                                              m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn);
+    m->launches++;
+    for (size_t n = 0; n < m->runs.size(); ++n) {
+        const RunInfo& R = m->runs[n];
+        const SmolLmLayer& L = m->layers[R.layer];
+        const int n_in = n_in_of(L);
+        CU(linear<T>(m, hn, static_cast<const T*>(L.w_in), proj, Tn, n_in, D, st));
+        int mix_cols;
+        if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
+            AttnArgs A;
+            A.proj = proj; A.n_in = n_in;
+            A.tok_seq = s->tok_seq; A.tok_pos = s->tok_pos; A.block_table = s->block_table;
+            A.max_pages = s->max_pages; A.page_size = c.page_size; A.n_pages = m->n_pages;
+            A.page_elems = m->page_elems; A.k_off = R.k_off; A.v_off = R.v_off;
+            A.H = L.heads; A.G = L.kv_heads; A.d = L.dim; A.dv = L.vdim;
+            A.scale = L.score_scale; A.eps = c.norm_eps;
+            A.q_norm = L.q_norm; A.k_norm = L.k_norm; A.r1 = L.dist_r1; A.r2 = L.dist_r2; A.sink = L.sink;
+            A.n_tokens = Tn; A.err = err;
+            const int units = Tn * (L.heads + 2 * L.kv_heads);
+            attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
+            const int au = Tn * L.heads;
+            attn_kernel<T><<<(au + kAttnWarps - 1) / kAttnWarps, kAttnWarps * 32, kAttnWarps * L.dim * sizeof(float), st>>>(A, qbuf, pool, mix);
+            m->launches += 2;
+            mix_cols = L.heads * L.vdim;
+        } else {
+            DeltaArgs A;
+            A.proj = proj; A.n_in = n_in; A.H = L.heads; A.d = L.dim; A.rank = L.rank; A.n_tokens = Tn;
+            A.decay_coef = L.decay_coef; A.unit_eps = L.unit_eps; A.eps = c.norm_eps;
+            A.rate_bias = L.rate_bias; A.decay_w2 = L.decay_w2; A.decay_bias = L.decay_bias; A.out_norm = L.out_norm;
+            A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
+            A.slot_floats = m->slot_floats; A.state_off = R.state_off; A.n_slots = m->n_slots; A.err = err;
+            delta_prep_kernel<<<Tn, 128, (L.rank + L.heads) * sizeof(float), st>>>(A, dec, uk, auk);
+            cudaError_t e;
+            if (L.dim <= 16) e = launch_scan<16, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
+            else if (L.dim <= 32) e = launch_scan<32, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
+            else if (L.dim <= 64) e = launch_scan<64, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
+            else e = launch_scan<128, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
+            CU(e);
+            m->launches += 2;
+            mix_cols = L.heads * L.dim;
+        }
+        CU(linear<T>(m, mix, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));
+        const bool last = n + 1 == m->runs.size();
+        const float* next_norm1 = last ? nullptr : m->layers[m->runs[n + 1].layer].norm1;
+        if (L.mlp == SMOL_LM_MLP_POLYNORM) {
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn);
+            CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
+            polynorm_kernel<T><<<Tn, 256, 0, st>>>(z, L.act, c.norm_eps, L.ff, act);
+            CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn);
+            m->launches += 3;
+        } else {
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn);
+            m->launches += 1;
+        }
+        if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    if (s->n_want > 0) {
+        norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
+        m->launches++;
+        CU(linear<T>(m, hw, static_cast<const T*>(m->g.head), s->logits, s->n_want, c.vocab, D, st));
+    }
+    CU(cudaGetLastError());
+    return SMOL_OK;
+}
+
+extern "C" int smol_lm_step(SmolLm* m, const SmolLmStep* s, void* stream) {
+    if (!m || !s) return fail(SMOL_ERR_INVALID, "smol_lm_step: null argument");
+    if (!m->bound) return fail(SMOL_ERR_UNBOUND, "smol_lm_step: bind weights and pools first");
+    if (s->n_tokens < 1 || s->n_seqs < 1 || s->n_want < 0 || s->max_pages < 1) return fail(SMOL_ERR_INVALID, "smol_lm_step: empty step");
+    if (s->n_tokens > m->cfg.max_step_tokens || s->n_seqs > m->cfg.max_step_seqs || s->n_want > m->cfg.max_want)
+        return fail(SMOL_ERR_CAPACITY, "smol_lm_step: step larger than the workspace was made for");
+    if (!s->tokens || !s->tok_seq || !s->tok_pos || !s->seq_start || !s->seq_pos0 || !s->seq_slot || !s->block_table ||
+        (s->n_want > 0 && (!s->want_rows || !s->logits)))
+        return fail(SMOL_ERR_INVALID, "smol_lm_step: null array");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return m->cfg.dtype == SMOL_LM_F32 ? step_impl<float>(m, s, st) : step_impl<bf16>(m, s, st);
+}
+
+extern "C" int smol_lm_linear(SmolLm* m, const void* d_a, const void* d_w, float* d_y, int32_t M, int32_t N, int32_t K, void* stream) {
+    if (!m || !d_a || !d_w || !d_y || M < 1 || N < 1 || K < 1) return fail(SMOL_ERR_INVALID, "smol_lm_linear: bad argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (m->cfg.dtype == SMOL_LM_F32) CU(linear<float>(m, static_cast<const float*>(d_a), static_cast<const float*>(d_w), d_y, M, N, K, st));
+    else CU(linear<bf16>(m, static_cast<const bf16*>(d_a), static_cast<const bf16*>(d_w), d_y, M, N, K, st));
+    return SMOL_OK;
+}
+
+extern "C" int smol_lm_sample(SmolLm* m, const float* d_logits, int32_t rows, int32_t n, float temp, int32_t top_k, float top_p,
+                              float min_p, uint64_t seed, const int32_t* d_seq_id, const int32_t* d_step, int32_t* d_out, void* stream) {
+    if (!m || !d_logits || !d_out || rows < 1) return fail(SMOL_ERR_INVALID, "smol_lm_sample: bad argument");
+    if (n < 1 || n > smol::kThreads * 64) return fail(SMOL_ERR_UNSUPPORTED, "smol_lm_sample: n outside [1, 32768]");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)n * sizeof(float);
+    const int grid = rows < 1024 ? rows : 1024;
+    if (n <= smol::kThreads * 8) {
+        CU(cudaFuncSetAttribute(lm_sample_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        lm_sample_kernel<8><<<grid, smol::kThreads, smem, st>>>(d_logits, n, rows, temp, top_k, top_p, min_p, seed, d_seq_id, d_step, d_out);
+    } else {
+        CU(cudaFuncSetAttribute(lm_sample_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        lm_sample_kernel<64><<<grid, smol::kThreads, smem, st>>>(d_logits, n, rows, temp, top_k, top_p, min_p, seed, d_seq_id, d_step, d_out);
+    }
+    CU(cudaGetLastError());
+    m->launches++;
+    return SMOL_OK;
+}

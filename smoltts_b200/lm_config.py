@@ -1,0 +1,156 @@
+"""Configuration of the hybrid language models (``config.json`` with an ``"architecture"`` key).
+
+A model is a list of layers; each layer names its token mixer (``type``) with the mixer's sizes and its feed-forward
+(``mlp`` or null).  ``loop`` repeats a span of layers with shared weights; every repetition ("layer run") owns its own
+key/value cache or recurrent state.  Every size and every constant that can differ between models is read from the
+file; what the design fixes is a class constant of the mixer's spec.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+MIXER_KINDS = {"attention": 0, "general_delta": 1}      # values of SMOL_LM_MIX_* (include/smoltts_b200_lm.h)
+MLP_KINDS = {None: 0, "dense": 1}                        # SMOL_LM_MLP_*: "dense" = up, PolyNorm, down
+
+
+@dataclass
+class MixerSpec:
+    kind: str
+    heads: int
+    dim: int
+    kv_heads: int = 0           # attention only
+    vdim: int = 0               # attention only
+    scale: float = 1.0          # attention only: multiplies q.k
+    # constants of the generalized delta rule (fixed by the design, parameters of the kernels)
+    decay_coef: float = math.exp(-0.5)
+    unit_eps: float = 1e-6
+
+    @classmethod
+    def from_dict(cls, kind: str, d: Dict[str, Any]) -> "MixerSpec":
+        if kind not in MIXER_KINDS:
+            raise ValueError(f"unknown mixer type {kind!r}; have {sorted(MIXER_KINDS)}")
+        if kind == "attention":
+            return cls(kind, int(d["heads"]), int(d["dim"]), int(d["kv_heads"]), int(d["vdim"]), float(d["scale"]))
+        return cls(kind, int(d["heads"]), int(d["dim"]), int(d["heads"]), int(d["dim"]))
+
+    def to_dict(self) -> Dict[str, Any]:
+        if self.kind == "attention":
+            return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        return {"heads": self.heads, "dim": self.dim}
+
+
+@dataclass
+class LayerSpec:
+    mixer: MixerSpec
+    mlp_kind: Optional[str] = None
+    ff: int = 0
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "LayerSpec":
+        mlp = d.get("mlp")
+        kind = mlp["kind"] if mlp else None
+        if kind not in MLP_KINDS:
+            raise ValueError(f"unknown feed-forward kind {kind!r}")
+        return cls(MixerSpec.from_dict(d["type"], d["mixer"]), kind, int(mlp["ff"]) if mlp else 0)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"type": self.mixer.kind, "mixer": self.mixer.to_dict(),
+                "mlp": {"kind": self.mlp_kind, "ff": self.ff} if self.mlp_kind else None}
+
+
+@dataclass
+class PamasunConfig:
+    architecture: str = "Pamasun"
+    vocab: int = 0
+    width: int = 0
+    embedding_scale: float = 1.0
+    norm_eps: float = 1e-5
+    layers: List[LayerSpec] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    extra: Dict[str, Any] = field(default_factory=dict, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "PamasunConfig":
+        loop = d.get("loop") or {}
+        known = {"architecture", "vocab", "width", "embedding", "norm", "layers", "loop"}
+        return cls(architecture=d.get("architecture", "Pamasun"), vocab=int(d["vocab"]), width=int(d["width"]),
+                   embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)),
+                   norm_eps=float((d.get("norm") or {}).get("eps", 1e-5)),
+                   layers=[LayerSpec.from_dict(x) for x in d["layers"]],
+                   loop_start=int(loop.get("start", 0)), loop_stop=int(loop.get("stop", 0)), loop_times=int(loop.get("times", 1)),
+                   extra={k: v for k, v in d.items() if k not in known})
+
+    @classmethod
+    def from_pretrained(cls, pathname: str) -> "PamasunConfig":
+        path = Path(pathname)
+        if path.is_dir():
+            path = path / "config.json"
+        with open(path, "r", encoding="utf-8") as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = dict(self.extra)
+        d.update(architecture=self.architecture, vocab=self.vocab, width=self.width, embedding={"scale": self.embedding_scale},
+                 norm={"eps": self.norm_eps}, layers=[x.to_dict() for x in self.layers],
+                 loop={"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times})
+        return d
+
+    def save(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.to_dict(), f, indent=1, sort_keys=True)
+
+    def layer_runs(self) -> List[int]:
+        """Layer index of every layer run, in execution order."""
+        n, a, b = len(self.layers), self.loop_start, self.loop_stop
+        if b <= a or self.loop_times == 1:
+            if self.loop_times < 1:
+                raise ValueError("loop.times must be at least 1")
+            return list(range(n))
+        if not (0 <= a < b <= n) or self.loop_times < 1:
+            raise ValueError(f"loop {a}..{b} x {self.loop_times} does not fit {n} layers")
+        return list(range(a)) + list(range(a, b)) * self.loop_times + list(range(b, n))
+
+    def tensor_shapes(self, rank_of: Optional[Dict[int, int]] = None) -> Dict[str, tuple]:
+        """Checkpoint tensor names and shapes.  The decay projection's inner size is not in the configuration: it is read
+        from the checkpoint (``rank_of[layer]``), 8 where unknown."""
+        D, V = self.width, self.vocab
+        out: Dict[str, tuple] = {"embed": (V, D), "head": (V, D), "final.norm": (D,)}
+        for i, L in enumerate(self.layers):
+            p, m = f"l{i}.", L.mixer
+            for nm in ("norm1", "norm1b", "ls1"):
+                out[p + nm] = (D,)
+            if m.kind == "attention":
+                out.update({p + "mix.q": (m.heads * m.dim, D), p + "mix.k": (m.kv_heads * m.dim, D), p + "mix.v": (m.kv_heads * m.vdim, D),
+                            p + "mix.g": (m.heads * m.vdim, D), p + "mix.o": (D, m.heads * m.vdim), p + "mix.q.norm": (m.dim,),
+                            p + "mix.k.norm": (m.dim,), p + "mix.r1": (m.heads,), p + "mix.r2": (m.heads,), p + "mix.sink": (m.heads,)})
+            else:
+                hd, rank = m.heads * m.dim, (rank_of or {}).get(i, 8)
+                for nm in ("r", "k", "v", "g", "a", "o"):
+                    out[p + "mix." + nm] = (hd, D) if nm != "o" else (D, hd)
+                out.update({p + "mix.a.b": (hd,), p + "mix.w1": (rank, D), p + "mix.w2": (hd, rank), p + "mix.w0": (hd,),
+                            p + "mix.norm": (hd,)})
+            if L.mlp_kind:
+                for nm in ("norm2", "norm2b", "ls2"):
+                    out[p + nm] = (D,)
+                out.update({p + "mlp.up": (L.ff, D), p + "mlp.down": (D, L.ff), p + "mlp.act": (4,)})
+        return out
+
+    # ---- accounting used by the benchmark ----
+    def weight_elements(self, rank: int = 8) -> int:
+        """Matrix elements one token touches (looped layers once: their weights are shared)."""
+        shapes = self.tensor_shapes({i: rank for i in range(len(self.layers))})
+        return sum(s[0] * s[1] for k, s in shapes.items() if len(s) == 2 and k != "embed")
+
+    def matmul_flops_per_token(self, rank: int = 8) -> int:
+        shapes = self.tensor_shapes({i: rank for i in range(len(self.layers))})
+        per_layer = [0] * len(self.layers)
+        for k, s in shapes.items():
+            if len(s) == 2 and k.startswith("l"):
+                per_layer[int(k[1:k.index(".")])] += 2 * s[0] * s[1]
+        return sum(per_layer[i] for i in self.layer_runs()) + 2 * self.vocab * self.width

@@ -26,6 +26,7 @@ import torch
 
 from . import _capi
 from .config import RQTransformerModelArgs
+from .pool import PagePool
 from .synth import TOK_IM_END, TOK_PAD, TOK_SEMANTIC0
 
 
@@ -183,7 +184,7 @@ class RQTransformer:
             self.page_bytes = self.lib.smol_kv_page_bytes(self._h)
             self._kv_pool = torch.zeros(self.n_pages * self.page_bytes, dtype=torch.uint8, device=self.device)
             _capi.check(self.lib.smol_kv_bind(self._h, C.c_void_p(self._kv_pool.data_ptr()), self.n_pages))
-        self._free_pages: List[int] = list(range(self.n_pages - 1, -1, -1))
+        self.page_pool = PagePool(self.n_pages, page_size)
         self._force: Optional[torch.Tensor] = None
         self._weights_struct = None
 
@@ -283,12 +284,10 @@ class RQTransformer:
 
     # ------------------------------------------------------------------ KV pages
     def allocate_pages(self, n: int) -> List[int]:
-        if n > len(self._free_pages):
-            raise _capi.SmolError(_capi.SMOL_ERR_CAPACITY, f"KV pool exhausted: need {n} pages, {len(self._free_pages)} free")
-        return [self._free_pages.pop() for _ in range(n)]
+        return self.page_pool.allocate(n)
 
     def free_pages(self, pages: Sequence[int]) -> None:
-        self._free_pages.extend(reversed(list(pages)))
+        self.page_pool.free(pages)
 
     def new_batch(self, batch: int, max_positions: Optional[int] = None, max_frames: int = 0,
                   seq_ids: Optional[Sequence[int]] = None) -> DecodeBatch:

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import collections
 import ctypes as C
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Deque, Dict, Iterator, List, Optional, Sequence, Tuple
 
 import torch
@@ -359,3 +359,182 @@ class ContinuousBatcher:
         uids = [self.submit(p, None if max_new_tokens is None else max_new_tokens[i]) for i, p in enumerate(prompts)]
         got: Dict[int, torch.Tensor] = dict(self.run())
         return [got[u] for u in uids]
+
+
+# ======================================================================================================================
+# Token-level continuous batching for the language-model engines (``lm.PamasunLM`` and whatever else implements
+# ``open_sequence / close_sequence / forward / sample``).
+@dataclass
+class _LmRequest:
+    uid: int
+    prompt: List[int]
+    budget: int
+    fed: int = 0                       # prompt tokens already in the cache
+    out: List[int] = field(default_factory=list)
+    seq: object = None
+
+
+class TokenBatcher:
+    """Continuous batching with chunked prefill: every step carries one decoded token for each running request plus, within
+    ``step_tokens``, the next portions of the prompts still being read -- so a long prompt never stalls the requests that are
+    decoding.  A request takes a state slot and key/value pages from the engine's pools when admitted and as it grows, and
+    gives them back when it retires; a request that does not fit waits in the queue.
+
+    ``feed`` is the step underneath (explicit token ids per request, logits back): generation calls it with the tokens it
+    sampled, a trace replayer with the tokens of its schedule."""
+
+    def __init__(self, model, temp: float = 0.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 0,
+                 step_tokens: Optional[int] = None, eos_id: Optional[int] = None):
+        self.model = model
+        self.temp, self.top_k, self.top_p, self.min_p, self.seed = temp, top_k, top_p, min_p, seed
+        self.step_tokens = min(step_tokens or model.max_step_tokens, model.max_step_tokens)
+        self.eos_id = eos_id
+        self._queue: Deque[_LmRequest] = collections.deque()
+        self._running: List[_LmRequest] = []
+        self._live: Dict[object, object] = {}     # uid -> engine sequence, for feed()
+        self._next_uid = 0
+        self.stats = {"steps": 0, "tokens": 0, "admitted": 0, "retired": 0}
+
+    # ---- explicit-token step (also the replayer's entry) ----
+    def feed(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]], end: Sequence[object] = (), trace: bool = False):
+        """entries: (request id, next token ids, wanted indices).  An unknown id is admitted.  Steps larger than the engine's
+        step capacity are run as several engine steps, cut at token boundaries.  Returns logits [n_want, vocab] fp32 on the
+        device (a fresh tensor), rows in the order of the entries.  ``end``: ids whose pages and slot are given back afterwards."""
+        model = self.model
+        for uid, _, _ in entries:
+            if uid not in self._live:
+                self._live[uid] = model.open_sequence(uid)
+                self.stats["admitted"] += 1
+        # reserve every page the step needs before running any part of it: a step either fits or fails as a whole
+        need = sum(model.page_pool.pages_for(self._live[u].length + len(t)) - len(self._live[u].pages) for u, t, _ in entries)
+        if need > len(model.page_pool):
+            raise _capi.SmolError(_capi.SMOL_ERR_CAPACITY, f"step needs {need} more pages, {len(model.page_pool)} free")
+        parts: List[List[Tuple[object, List[int], List[int]]]] = [[]]
+        room = self.step_tokens
+        perm: List[int] = []                      # output row -> row in the order the parts produce them
+        for uid, toks, want in entries:
+            toks, want, lo = list(toks), list(want), 0
+            by_place = sorted(range(len(want)), key=lambda k: want[k])
+            inverse = [0] * len(want)
+            for produced, k in enumerate(by_place):
+                inverse[k] = len(perm) + produced
+            perm_entry = inverse
+            want = [want[k] for k in by_place]
+            perm.extend(perm_entry)
+            while lo < len(toks):
+                if room == 0 or len(parts[-1]) >= model.max_seqs:
+                    parts.append([])
+                    room = self.step_tokens
+                hi = min(len(toks), lo + room)
+                parts[-1].append((self._live[uid], toks[lo:hi], [w - lo for w in want if lo <= w < hi]))
+                room -= hi - lo
+                lo = hi
+        outs, traces = [], []
+        for part in parts:
+            res = model.forward(part, trace=trace)
+            if trace:
+                res, tr = res
+                traces.append(tr)
+            if res.shape[0]:
+                outs.append(res.clone())
+            self.stats["steps"] += 1
+            self.stats["tokens"] += sum(len(t) for _, t, _ in part)
+        for uid in end:
+            seq = self._live.pop(uid, None)
+            if seq is not None:
+                model.close_sequence(seq)
+                self.stats["retired"] += 1
+        logits = torch.cat(outs, 0) if outs else torch.empty(0, model.config.vocab, device=model.device)
+        if perm != list(range(len(perm))):
+            logits = logits[torch.tensor(perm, device=logits.device)]
+        return (logits, traces) if trace else logits
+
+    # ---- generation ----
+    def submit(self, prompt: Sequence[int], max_new_tokens: int = 16, uid: Optional[int] = None) -> int:
+        if len(prompt) < 1:
+            raise ValueError("a prompt needs at least one token")
+        if uid is None:
+            uid = self._next_uid
+        self._next_uid = max(self._next_uid, uid) + 1
+        self._queue.append(_LmRequest(uid, [int(t) for t in prompt], int(max_new_tokens)))
+        return uid
+
+    @property
+    def pending(self) -> int:
+        return len(self._queue)
+
+    @property
+    def running(self) -> int:
+        return len(self._running)
+
+    def _admit(self) -> None:
+        model = self.model
+        while self._queue and len(self._running) < model.max_seqs and len(model.slot_pool) > 0:
+            req = self._queue[0]
+            # admit only if the pool can hold the whole request next to what the running ones may still grow by
+            reserved = sum(model.page_pool.pages_for(len(r.prompt) + r.budget) - len(r.seq.pages) for r in self._running)
+            if model.page_pool.pages_for(len(req.prompt) + req.budget) + reserved > len(model.page_pool):
+                if not self._running:
+                    raise _capi.SmolError(_capi.SMOL_ERR_CAPACITY, f"request {req.uid} does not fit the key/value pool")
+                break
+            self._queue.popleft()
+            req.seq = model.open_sequence(req.uid)
+            self._live[req.uid] = req.seq
+            self._running.append(req)
+            self.stats["admitted"] += 1
+
+    def step(self) -> List[Tuple[int, List[int]]]:
+        """Admit what fits, run one engine step, sample, retire; returns the requests that finished as (uid, new tokens)."""
+        self._admit()
+        if not self._running:
+            return []
+        entries, samplers = [], []
+        room = self.step_tokens
+        for r in self._running:                              # decoding requests first: one token each
+            if r.fed == len(r.prompt) and room > 0:
+                entries.append((r.uid, [r.out[-1]], [0]))
+                samplers.append(r)
+                room -= 1
+        for r in self._running:                              # then portions of prompts
+            if r.fed < len(r.prompt) and room > 0:
+                n = min(room, len(r.prompt) - r.fed)
+                last = r.fed + n == len(r.prompt)
+                entries.append((r.uid, r.prompt[r.fed:r.fed + n], [n - 1] if last else []))
+                r.fed += n
+                room -= n
+                if last:
+                    samplers.append(r)
+        logits = self.feed(entries)
+        done: List[Tuple[int, List[int]]] = []
+        if samplers:
+            dev = self.model.device
+            ids = torch.tensor([r.uid for r in samplers], dtype=torch.int32, device=dev)
+            steps = torch.tensor([len(r.out) for r in samplers], dtype=torch.int32, device=dev)
+            picked = self.model.sample(logits, self.temp, self.top_k, self.top_p, self.min_p, self.seed, ids, steps).cpu().tolist()
+            for r, tok in zip(samplers, picked):
+                r.out.append(int(tok))
+                if len(r.out) >= r.budget or (self.eos_id is not None and tok == self.eos_id):
+                    done.append((r.uid, r.out))
+        for uid, _ in done:
+            r = next(x for x in self._running if x.uid == uid)
+            self._running.remove(r)
+            self.model.close_sequence(self._live.pop(uid))
+            self.stats["retired"] += 1
+        return done
+
+    def run(self) -> Iterator[Tuple[int, List[int]]]:
+        while self._queue or self._running:
+            for item in self.step():
+                yield item
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16) -> List[List[int]]:
+        """Submit every prompt, run to completion, return the new tokens in the callers' order."""
+        uids = [self.submit(p, max_new_tokens) for p in prompts]
+        got = dict(self.run())
+        return [got[u] for u in uids]
+
+    def close(self) -> None:
+        for seq in self._live.values():
+            self.model.close_sequence(seq)
+        self._live.clear()
+        self._running = []

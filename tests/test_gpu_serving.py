@@ -39,7 +39,7 @@ def test_continuous_batcher_equals_generate_batch(size, slots, sampled):
                             top_p=0.9 if sampled else 1.0, seed=11, max_new_tokens=23)
     uids = [100 + i for i in range(n)]
     want = _reference(model, prompts, budgets, gs, slots, uids)
-    free0 = len(model._free_pages)
+    free0 = len(model.page_pool)
     cb = ContinuousBatcher(model, gs, slots=slots, max_prompt=64, chunk=4, audio_only=False, ignore_stop=True)
     for i in range(n):
         cb.submit(prompts[i], max_new_tokens=budgets[i] - 1, uid=uids[i])
@@ -56,7 +56,7 @@ def test_continuous_batcher_equals_generate_batch(size, slots, sampled):
     assert cb.stats["admitted"] == cb.stats["retired"] == n
     assert cb.stats["frames_decoded"] < cb.stats["slot_frames"]        # the tail of the run has idle slots
     cb.close()
-    assert len(model._free_pages) == free0, "every KV page must be back in the pool"
+    assert len(model.page_pool) == free0, "every KV page must be back in the pool"
 
 
 def test_pages_are_recycled_under_a_small_pool():

@@ -7,8 +7,12 @@ import re
 from conftest import ROOT
 
 
-def _declared():
-    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in sorted(os.listdir(os.path.join(ROOT, "include"))) if h.endswith(".h"))
+LM_HEADER = "smoltts_b200_lm.h"      # declares the symbols of libsmoltts_b200_lm.so; every other header belongs to the core library
+
+
+def _declared(lm: bool = False):
+    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in sorted(os.listdir(os.path.join(ROOT, "include")))
+                   if h.endswith(".h") and (h == LM_HEADER) == lm)
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(smol_[a-z_0-9]+)\s*\(", text)))
 
@@ -25,6 +29,35 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), f"{n} declared in the header but not exported by {path}"
     assert set(names) == set(_capi.PROTOTYPES), (set(names) ^ set(_capi.PROTOTYPES))
     assert _capi.load().smol_abi_version() == _capi.SMOL_ABI_VERSION
+
+
+def test_lm_library_exports_every_declared_symbol_and_validates_on_create():
+    from smoltts_b200 import _capi_lm, build
+
+    path = build.build(target="lm")
+    lib = ctypes.CDLL(path)
+    names = _declared(lm=True)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported by {path}"
+    assert set(names) == set(_capi_lm.PROTOTYPES), (set(names) ^ set(_capi_lm.PROTOTYPES))
+    lib = _capi_lm.load()
+    cfg = _capi_lm.SmolLmConfig(dtype=0, vocab=64, width=32, n_layers=2, n_runs=3, page_size=16, max_step_tokens=64, max_step_seqs=2,
+                                max_want=8, embed_scale=1.0, norm_eps=1e-5)
+    layers = (_capi_lm.SmolLmLayer * 2)()
+    layers[0].mixer, layers[0].heads, layers[0].kv_heads, layers[0].dim, layers[0].vdim = 0, 4, 2, 8, 24
+    layers[1].mixer, layers[1].heads, layers[1].kv_heads, layers[1].dim, layers[1].vdim, layers[1].rank = 1, 2, 2, 16, 16, 4
+    runs = (ctypes.c_int32 * 3)(0, 1, 0)
+    h = ctypes.c_void_p()
+    assert lib.smol_lm_create(ctypes.byref(cfg), layers, runs, ctypes.byref(h)) == 0
+    # a page: two attention runs x (2 kv heads x 16 positions x (8 + 24)) bf16; a slot: one recurrent run of 2 heads x 16 x 16 fp32
+    assert lib.smol_lm_page_bytes(h) == 2 * 2 * 16 * 32 * 2 and lib.smol_lm_slot_bytes(h) == 2 * 16 * 16 * 4
+    step = _capi_lm.SmolLmStep()
+    assert lib.smol_lm_step(h, ctypes.byref(step), None) == -2 and b"bind" in lib.smol_lm_last_error()
+    lib.smol_lm_destroy(h)
+    layers[0].kv_heads = 3
+    assert lib.smol_lm_create(ctypes.byref(cfg), layers, runs, ctypes.byref(h)) == -1
+    layers[0].kv_heads, layers[1].dim = 2, 160
+    assert lib.smol_lm_create(ctypes.byref(cfg), layers, runs, ctypes.byref(h)) == -4
 
 
 def test_create_validates_shapes_without_a_gpu():

@@ -111,6 +111,10 @@ def parse_args():
     ap.add_argument("--stream-lm-ctas", type=int, default=96, help="tts_stream_bs1: CTAs of the decode kernel while the codec runs beside it")
     ap.add_argument("--no-stream-overlap", action="store_true", help="tts_stream_bs1: codec step after the decode step instead of beside the next one")
     ap.add_argument("--cpu-frames", type=int, default=0, help="frames of the CPU sample (0 = %d)" % CPU_SAMPLE_FRAMES)
+    ap.add_argument("--lm", action="store_true", help="instead of the default workload: prefill / decode tokens/s of the hybrid "
+                    "language-model engine at a few layer sizes beside the DualAR slow transformer (smoltts_b200/lm_bench.py)")
+    ap.add_argument("--lm-sizes", default="", help="--lm: comma list of sizes (default: all of lm_bench.SIZES)")
+    ap.add_argument("--lm-prompt", type=int, default=2048, help="--lm: prompt tokens / cached context")
     ap.add_argument("--opt", action="append", default=[], help="engine option name=value (smol_set_option), repeatable")
     return ap.parse_args()
 
@@ -718,7 +722,11 @@ def run_ours(args):
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.lm:
+        from smoltts_b200 import lm_bench
+
+        lm_bench.run(args, ROOT)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

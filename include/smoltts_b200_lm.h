@@ -65,6 +65,7 @@ typedef struct SmolLmConfig {
     int32_t max_step_tokens;  /* rows of the workspace: most tokens one step may bring */
     int32_t max_step_seqs;    /* most sequences in one step */
     int32_t max_want;         /* most logits rows asked for in one step */
+    int32_t max_context;      /* most positions one sequence may hold (sizes the scratch of the few-token attention path) */
     float embed_scale, norm_eps;
 } SmolLmConfig;
 
@@ -77,6 +78,9 @@ typedef struct SmolLmGlobals {
 /* A ragged batch.  All arrays live on the device. */
 typedef struct SmolLmStep {
     int32_t n_tokens, n_seqs, n_want, max_pages;
+    /* what the host knows about the step, used to choose kernels and grids (0 = unknown: the safe choice is made):
+     * fewest / most tokens any sequence brings, and the largest position in the step */
+    int32_t min_seq_tokens, max_seq_tokens, max_pos;
     const int32_t* tokens;       /* [n_tokens] ids, sequences one after the other */
     const int32_t* tok_seq;      /* [n_tokens] index of the token's sequence in this step */
     const int32_t* tok_pos;      /* [n_tokens] position in its sequence, counted from 0 */

@@ -25,7 +25,7 @@ class SmolLmLayer(C.Structure):
 
 class SmolLmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
-                                         "max_step_seqs", "max_want")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
+                                         "max_step_seqs", "max_want", "max_context")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
 
 
 class SmolLmGlobals(C.Structure):
@@ -33,7 +33,7 @@ class SmolLmGlobals(C.Structure):
 
 
 class SmolLmStep(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "n_seqs", "n_want", "max_pages")] + [
+    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "n_seqs", "n_want", "max_pages", "min_seq_tokens", "max_seq_tokens", "max_pos")] + [
         (n, C.c_void_p) for n in ("tokens", "tok_seq", "tok_pos", "seq_start", "seq_pos0", "seq_slot", "block_table", "want_rows",
                                   "logits", "trace")]
 

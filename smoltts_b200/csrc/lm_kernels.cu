@@ -293,6 +293,39 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
         }
 }
 
+// Matrix product for very few rows (decoding): one warp per output column, lanes cut K into 16-byte pieces; the weights are
+// streamed once, the MR activation rows come from L1/L2.  Needs K % 8 == 0 and 16-byte aligned operands.
+template <int MR>
+__global__ void __launch_bounds__(256) gemv_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ y,
+                                                        int M, int N, int K) {
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.0f;
+    const bf16* wr = w + (size_t)n * K;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = ldg_stream(wr + k);
+        const float w0 = bf_lo(wv.x), w1 = bf_hi(wv.x), w2 = bf_lo(wv.y), w3 = bf_hi(wv.y), w4 = bf_lo(wv.z), w5 = bf_hi(wv.z),
+                    w6 = bf_lo(wv.w), w7 = bf_hi(wv.w);
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            if (m < M) {
+                const uint4 av = ldg_v4(a + (size_t)m * K + k);
+                float t = acc[m];
+                t = fmaf(bf_lo(av.x), w0, t); t = fmaf(bf_hi(av.x), w1, t); t = fmaf(bf_lo(av.y), w2, t); t = fmaf(bf_hi(av.y), w3, t);
+                t = fmaf(bf_lo(av.z), w4, t); t = fmaf(bf_hi(av.z), w5, t); t = fmaf(bf_lo(av.w), w6, t); t = fmaf(bf_hi(av.w), w7, t);
+                acc[m] = t;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+        const float t = warp_sum(acc[m]);
+        if (lane == 0 && m < M) y[(size_t)m * N + n] = t;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Attention with a sink.  proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv].
 struct AttnArgs {
@@ -306,6 +339,9 @@ struct AttnArgs {
     const float *q_norm, *k_norm, *r1, *r2, *sink;
     int n_tokens;
     int32_t* err;
+    const int32_t* seq_start;
+    int split_len, n_splits, short_rows;   // few-token path: key range per block, ranges per row, rows = sequences x kShortSeq
+    float* part;                           // [short_rows][H][n_splits][dv + 2]: running maximum, denominator, unnormalised output
 };
 
 // One warp per (token, slot): slots 0..H-1 norm a query head into qbuf, H..H+G-1 norm a key head into the pool,
@@ -418,6 +454,279 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Attention for sequences that bring few tokens (decoding, short portions): the keys of a row are cut into fixed
+// ranges of A.split_len positions, one block per (row, key/value head, range), whose warps take the query heads of
+// that key/value head; a second kernel merges the ranges with the sink and applies the gate.  The ranges are absolute
+// positions, so a row's result does not depend on what else is in the step.
+constexpr int kShortSeq = 8;          // a sequence with at most this many tokens in a step takes this path
+
+template <class T>
+__global__ void __launch_bounds__(128) attn_split_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool) {
+    extern __shared__ float qs_all[];
+    const int s = blockIdx.x / kShortSeq, r = blockIdx.x % kShortSeq;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    if (n > kShortSeq || r >= n) return;
+    const int t = t0 + r, pos = A.tok_pos[t];
+    const int j_lo = blockIdx.z * A.split_len;
+    if (j_lo > pos) return;
+    const int j_hi = min(pos, j_lo + A.split_len - 1);
+    const int g = blockIdx.y, Gq = A.H / A.G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
+    float* qs = qs_all + warp * A.d;
+    for (int hq = warp; hq < Gq; hq += 4) {
+        const int h = g * Gq + hq;
+        __syncwarp();
+        for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
+        __syncwarp();
+        const float r1 = A.r1[h], r2 = A.r2[h];
+        float m = -INFINITY, l = 0.0f;
+        float o[kAttnMaxV];
+#pragma unroll
+        for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+        for (int j0 = j_lo; j0 <= j_hi; j0 += 32) {
+            const int j = j0 + lane;
+            float sc = -INFINITY;
+            const T* vrow = nullptr;
+            if (j <= j_hi) {
+                const int page = bt[j / A.page_size], in_pg = j % A.page_size;
+                const T* base = pool + (size_t)page * A.page_elems;
+                const T* k = base + A.k_off + ((size_t)g * A.page_size + in_pg) * A.d;
+                vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv;
+                float dot = 0.0f;
+                for (int c = 0; c < A.d; ++c) dot = fmaf(qs[c], to_f<T>(k[c]), dot);
+                sc = dot * A.scale - r1 * log1pf(r2 * (float)(pos - j));
+            }
+            const float mn = fmaxf(m, warp_max(sc));          // finite: lane 0 of every round holds a valid key
+            const float p = (j <= j_hi) ? expf(sc - mn) : 0.0f;
+            const float corr = expf(m - mn);
+            l = l * corr + warp_sum(p);
+            m = mn;
+#pragma unroll
+            for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
+            const int cnt = min(32, j_hi - j0 + 1);
+            for (int jj = 0; jj < cnt; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const T* vr = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(vrow), jj));
+#pragma unroll
+                for (int e = 0; e < kAttnMaxV; ++e) {
+                    const int c = lane + e * 32;
+                    if (c < A.dv) o[e] = fmaf(pj, to_f<T>(vr[c]), o[e]);
+                }
+            }
+        }
+        float* dst = A.part + (((size_t)blockIdx.x * A.H + h) * A.n_splits + blockIdx.z) * (A.dv + 2);
+        if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+        for (int e = 0; e < kAttnMaxV; ++e) {
+            const int c = lane + e * 32;
+            if (c < A.dv) dst[2 + c] = o[e];
+        }
+    }
+}
+
+// One warp per (row, query head): merges the ranges; the sink enters here, once, with no value.
+template <class T>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (unit >= A.short_rows * A.H) return;
+    const int x = unit / A.H, h = unit % A.H;
+    const int s = x / kShortSeq, r = x % kShortSeq;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    if (n > kShortSeq || r >= n) return;
+    const int t = t0 + r, pos = A.tok_pos[t];
+    const int ns = pos / A.split_len + 1;
+    const float* src = A.part + ((size_t)x * A.H + h) * A.n_splits * (A.dv + 2);
+    float M = A.sink[h];
+    for (int z = 0; z < ns; ++z) M = fmaxf(M, src[(size_t)z * (A.dv + 2)]);
+    float l = expf(A.sink[h] - M);
+    float o[kAttnMaxV];
+#pragma unroll
+    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+    for (int z = 0; z < ns; ++z) {
+        const float* p = src + (size_t)z * (A.dv + 2);
+        const float w = expf(p[0] - M);
+        l = fmaf(p[1], w, l);
+#pragma unroll
+        for (int e = 0; e < kAttnMaxV; ++e) {
+            const int c = lane + e * 32;
+            if (c < A.dv) o[e] = fmaf(p[2 + c], w, o[e]);
+        }
+    }
+    const float inv = 1.0f / l;
+    const float* gate = A.proj + (size_t)t * A.n_in + A.H * A.d + A.G * A.d + A.G * A.dv + h * A.dv;
+#pragma unroll
+    for (int e = 0; e < kAttnMaxV; ++e) {
+        const int c = lane + e * 32;
+        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * sigmoidf_(gate[c]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention for prompt portions, bf16, on the tensor cores (mma.sync m16n8k16, fp32 accumulation).  One block per
+// (64-row tile of a sequence's rows in this step, sequence, query head); each of the four warps owns 16 rows.  Keys and
+// values are staged 64 positions at a time from the paged pool into shared memory (head sizes padded with zeros to DP).
+// Scores, the distance penalty, the running maximum and the softmax weights are fp32; for the weights x values product a
+// weight is split into a bf16 head and a bf16 remainder (two MMAs), which keeps 16 mantissa bits of it.  The sink is
+// the initial state of the running softmax: maximum = sink, denominator = 1.
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+
+// rows x cols bf16 from `src(row)` (nullptr: a row of zeros) into dst[row * LD + col], columns cols .. DP-1 zeroed.
+template <int DP, class RowPtr>
+__device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
+    constexpr int LD = DP + 8;
+    const bool vec = (cols % 8) == 0;
+    for (int idx = threadIdx.x; idx < 64 * (DP / 8); idx += 128) {
+        const int row = idx / (DP / 8), c = (idx % (DP / 8)) * 8;
+        const bf16* p = src(row);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (p && c < cols) {
+            if (vec && (reinterpret_cast<uintptr_t>(p) % 16) == 0) {
+                v = *reinterpret_cast<const uint4*>(p + c);
+            } else {
+                uint16_t hh[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hh[e] = (c + e < cols) ? reinterpret_cast<const uint16_t*>(p)[c + e] : (uint16_t)0;
+                v.x = hh[0] | ((uint32_t)hh[1] << 16); v.y = hh[2] | ((uint32_t)hh[3] << 16);
+                v.z = hh[4] | ((uint32_t)hh[5] << 16); v.w = hh[6] | ((uint32_t)hh[7] << 16);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + row * LD + c) = v;
+    }
+}
+
+template <int DP>
+__global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const bf16* __restrict__ qbuf, const bf16* __restrict__ pool,
+                                                         bf16* __restrict__ out) {
+    constexpr int LD = DP + 8;
+    __shared__ __align__(16) bf16 Ks[64 * LD];
+    __shared__ __align__(16) bf16 Vs[64 * LD];
+    const int s = blockIdx.y;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    const int tile = blockIdx.x;
+    if (n <= kShortSeq || tile * 64 >= n) return;
+    const int h = blockIdx.z, g = h / (A.H / A.G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int pos0 = A.tok_pos[t0];
+    const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
+    // queries of the tile -> A fragments
+    stage_rows<DP>(Ks, A.d, [&](int row) -> const bf16* {
+        return tile * 64 + row < n ? qbuf + ((size_t)(t0 + tile * 64 + row) * A.H + h) * A.d : nullptr;
+    });
+    __syncthreads();
+    uint32_t qf[DP / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+        const bf16* p = Ks + (warp * 16 + gq) * LD + kk * 16 + tq * 2;
+        qf[kk][0] = *reinterpret_cast<const uint32_t*>(p);
+        qf[kk][1] = *reinterpret_cast<const uint32_t*>(p + 8 * LD);
+        qf[kk][2] = *reinterpret_cast<const uint32_t*>(p + 8);
+        qf[kk][3] = *reinterpret_cast<const uint32_t*>(p + 8 * LD + 8);
+    }
+    __syncthreads();
+    const int row_a = tile * 64 + warp * 16 + gq, row_b = row_a + 8;
+    const int i_a = pos0 + row_a, i_b = pos0 + row_b;
+    const int last_pos = pos0 + min(n, tile * 64 + 64) - 1;
+    const float r1 = A.r1[h], r2 = A.r2[h], sink = A.sink[h];
+    float m_a = sink, m_b = sink, l_a = tq == 0 ? 1.0f : 0.0f, l_b = l_a;
+    float o[DP / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < DP / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[nt][e] = 0.0f;
+    for (int j0 = 0; j0 <= last_pos; j0 += 64) {
+        auto row_of = [&](int row, size_t off, int width) -> const bf16* {
+            const int j = j0 + row;
+            if (j > last_pos) return nullptr;
+            return pool + (size_t)bt[j / A.page_size] * A.page_elems + off + ((size_t)g * A.page_size + j % A.page_size) * width;
+        };
+        stage_rows<DP>(Ks, A.d, [&](int row) { return row_of(row, A.k_off, A.d); });
+        stage_rows<DP>(Vs, A.dv, [&](int row) { return row_of(row, A.v_off, A.dv); });
+        __syncthreads();
+        if (j0 <= pos0 + tile * 64 + warp * 16 + 15) {          // this warp's rows see at least one key of the tile
+            float S[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) S[nt][e] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < DP / 16; ++kk)
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    const bf16* p = Ks + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
+                    mma_bf16_16816(S[nt], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], *reinterpret_cast<const uint32_t*>(p),
+                                   *reinterpret_cast<const uint32_t*>(p + 8));
+                }
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + nt * 8 + tq * 2 + (e & 1);
+                    const int i = e < 2 ? i_a : i_b;
+                    const float v = j <= i ? S[nt][e] * A.scale - r1 * log1pf(r2 * (float)(i - j)) : -INFINITY;
+                    S[nt][e] = v;
+                    if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float ca = expf(m_a - mn_a), cb = expf(m_b - mn_b);
+            m_a = mn_a; m_b = mn_b;
+            l_a *= ca; l_b *= cb;
+#pragma unroll
+            for (int nt = 0; nt < DP / 8; ++nt) { o[nt][0] *= ca; o[nt][1] *= ca; o[nt][2] *= cb; o[nt][3] *= cb; }
+            uint32_t hi[8][2], lo[8][2];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) p[e] = expf(S[nt][e] - (e < 2 ? mn_a : mn_b));
+                l_a += p[0] + p[1];
+                l_b += p[2] + p[3];
+                float ph[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ph[e] = bf16_round(p[e]);
+                hi[nt][0] = pack_bf16(ph[0], ph[1]); hi[nt][1] = pack_bf16(ph[2], ph[3]);
+                lo[nt][0] = pack_bf16(p[0] - ph[0], p[1] - ph[1]); lo[nt][1] = pack_bf16(p[2] - ph[2], p[3] - ph[3]);
+            }
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2)
+#pragma unroll
+                for (int nt = 0; nt < DP / 8; ++nt) {
+                    uint32_t b0, b1;
+                    ldmatrix_x2_trans(b0, b1, Vs + (k2 * 16 + (lane & 15)) * LD + nt * 8);
+                    mma_bf16_16816(o[nt], hi[2 * k2][0], hi[2 * k2][1], hi[2 * k2 + 1][0], hi[2 * k2 + 1][1], b0, b1);
+                    mma_bf16_16816(o[nt], lo[2 * k2][0], lo[2 * k2][1], lo[2 * k2 + 1][0], lo[2 * k2 + 1][1], b0, b1);
+                }
+        }
+        __syncthreads();
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
+    const size_t goff = (size_t)A.H * A.d + A.G * A.d + A.G * A.dv + (size_t)h * A.dv;
+#pragma unroll
+    for (int nt = 0; nt < DP / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int row = e < 2 ? row_a : row_b, c = nt * 8 + tq * 2 + (e & 1);
+            if (row < n && c < A.dv) {
+                const size_t t = t0 + row;
+                out[(t * A.H + h) * A.dv + c] = __float2bfloat16_rn(o[nt][e] * (e < 2 ? inv_a : inv_b) * sigmoidf_(A.proj[t * A.n_in + goff + c]));
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // Generalized delta rule.  proj row layout: r | k | v | gate | rate (each H*d), then the decay's inner vector [rank].
 struct DeltaArgs {
     const float* proj;
@@ -458,17 +767,19 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
     }
 }
 
-// The recurrence.  One block per (sequence, head); thread j owns value column j of the state, S[i] = state[i][j] in
-// registers (DK >= d key channels; channels beyond d are padded with zero keys).  Tokens are staged through shared
+// The recurrence.  One block per (sequence, head).  Four adjacent lanes share value column j of the state: lane q of
+// the four keeps rows q*R .. q*R+R-1 (R = DK / 4, DK >= d key channels; channels beyond d are padded with zero keys) in
+// registers, and the two sums over key channels are finished with two shuffles each.  Tokens are staged through shared
 // memory kDeltaChunk at a time.  Per token:  seen = sum_i u_i S_i;  S_i <- w_i S_i - (a u)_i seen + k_i v_j;
 // o_j = sum_i S_i r_i.  The epilogue divides each head's o by its root mean square, applies the plain weight and the
 // sigmoid gate, and writes the mixer's output in T.
-constexpr int kDeltaChunk = 8;
+constexpr int kDeltaChunk = 16;
 
 template <int DK, class T>
-__global__ void delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay, const float* __restrict__ ukey,
-                                  const float* __restrict__ aukey, float* __restrict__ state_pool, T* __restrict__ out) {
-    extern __shared__ float sh[];
+__global__ void __launch_bounds__(DK * 4) delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay, const float* __restrict__ ukey,
+                                                           const float* __restrict__ aukey, float* __restrict__ state_pool, T* __restrict__ out) {
+    constexpr int R = DK / 4;
+    extern __shared__ __align__(16) float sh[];
     const int d = A.d, HD = A.H * d;
     float* s_r = sh;                             // [chunk][DK] each
     float* s_k = s_r + kDeltaChunk * DK;
@@ -477,20 +788,23 @@ __global__ void delta_scan_kernel(const DeltaArgs A, const float* __restrict__ d
     float* s_w = s_au + kDeltaChunk * DK;
     float* s_red = s_w + kDeltaChunk * DK;       // [warps][chunk]
     const int seq = blockIdx.x / A.H, h = blockIdx.x % A.H;
-    const int j = threadIdx.x;
+    const int j = threadIdx.x >> 2, q = threadIdx.x & 3;
     const bool live = j < d;
-    const int nw = (blockDim.x + 31) >> 5, warp = j >> 5, lane = j & 31;
+    const int nw = (blockDim.x + 31) >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = A.seq_start[seq], t1 = A.seq_start[seq + 1];
     const int slot = A.seq_slot[seq];
     if (slot < 0 || slot >= A.n_slots) {
-        if (j == 0) atomicExch(A.err, 2);
+        if (threadIdx.x == 0) atomicExch(A.err, 2);
         return;
     }
     float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * d;
-    float S[DK];
+    float S[R];
     const bool fresh = A.seq_pos0[seq] == 0;
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[i] = (live && !fresh && i < d) ? st[(size_t)i * d + j] : 0.0f;
+    for (int e = 0; e < R; ++e) {
+        const int i = q * R + e;
+        S[e] = (live && !fresh && i < d) ? st[(size_t)i * d + j] : 0.0f;
+    }
     for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
         const int n = min(kDeltaChunk, t1 - c0);
         __syncthreads();
@@ -511,33 +825,47 @@ __global__ void delta_scan_kernel(const DeltaArgs A, const float* __restrict__ d
             o[tt] = 0.0f;
             if (tt < n) {
                 const float v = live ? A.proj[(size_t)(c0 + tt) * A.n_in + 2 * HD + h * d + j] : 0.0f;
-                const float *pr = s_r + tt * DK, *pk = s_k + tt * DK, *pu = s_u + tt * DK, *pa = s_au + tt * DK, *pw = s_w + tt * DK;
-                float seen0 = 0.0f, seen1 = 0.0f;
+                const int base = tt * DK + q * R;
+                float seen = 0.0f;
 #pragma unroll
-                for (int i = 0; i < DK; i += 2) {
-                    seen0 = fmaf(pu[i], S[i], seen0);
-                    seen1 = fmaf(pu[i + 1], S[i + 1], seen1);
+                for (int e = 0; e < R; e += 4) {
+                    const float4 u4 = *reinterpret_cast<const float4*>(s_u + base + e);
+                    seen = fmaf(u4.x, S[e], seen);
+                    seen = fmaf(u4.y, S[e + 1], seen);
+                    seen = fmaf(u4.z, S[e + 2], seen);
+                    seen = fmaf(u4.w, S[e + 3], seen);
                 }
-                const float seen = seen0 + seen1;
-                float acc0 = 0.0f, acc1 = 0.0f;
+                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                float acc = 0.0f;
 #pragma unroll
-                for (int i = 0; i < DK; i += 2) {
-                    S[i] = fmaf(pk[i], v, fmaf(pw[i], S[i], -pa[i] * seen));
-                    S[i + 1] = fmaf(pk[i + 1], v, fmaf(pw[i + 1], S[i + 1], -pa[i + 1] * seen));
-                    acc0 = fmaf(S[i], pr[i], acc0);
-                    acc1 = fmaf(S[i + 1], pr[i + 1], acc1);
+                for (int e = 0; e < R; e += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(s_w + base + e);
+                    const float4 a4 = *reinterpret_cast<const float4*>(s_au + base + e);
+                    const float4 k4 = *reinterpret_cast<const float4*>(s_k + base + e);
+                    const float4 r4 = *reinterpret_cast<const float4*>(s_r + base + e);
+                    S[e] = fmaf(k4.x, v, fmaf(w4.x, S[e], -a4.x * seen));
+                    S[e + 1] = fmaf(k4.y, v, fmaf(w4.y, S[e + 1], -a4.y * seen));
+                    S[e + 2] = fmaf(k4.z, v, fmaf(w4.z, S[e + 2], -a4.z * seen));
+                    S[e + 3] = fmaf(k4.w, v, fmaf(w4.w, S[e + 3], -a4.w * seen));
+                    acc = fmaf(S[e], r4.x, acc);
+                    acc = fmaf(S[e + 1], r4.y, acc);
+                    acc = fmaf(S[e + 2], r4.z, acc);
+                    acc = fmaf(S[e + 3], r4.w, acc);
                 }
-                o[tt] = acc0 + acc1;
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                o[tt] = acc;
             }
         }
-        // per-head mean of o^2 for every token of the chunk
+        // per-head mean of o^2 for every token of the chunk (each column counted once: by its lane 0)
 #pragma unroll
         for (int tt = 0; tt < kDeltaChunk; ++tt) {
-            const float q = warp_sum(live ? o[tt] * o[tt] : 0.0f);
-            if (lane == 0) s_red[warp * kDeltaChunk + tt] = q;
+            const float sq = warp_sum((live && q == 0) ? o[tt] * o[tt] : 0.0f);
+            if (lane == 0) s_red[warp * kDeltaChunk + tt] = sq;
         }
         __syncthreads();
-        if (live) {
+        if (live && q == 0) {
             const float nwgt = A.out_norm[h * d + j];
 #pragma unroll
             for (int tt = 0; tt < kDeltaChunk; ++tt) {
@@ -553,8 +881,10 @@ __global__ void delta_scan_kernel(const DeltaArgs A, const float* __restrict__ d
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i)
-            if (i < d) st[(size_t)i * d + j] = S[i];
+        for (int e = 0; e < R; ++e) {
+            const int i = q * R + e;
+            if (i < d) st[(size_t)i * d + j] = S[e];
+        }
     }
 }
 
@@ -610,7 +940,8 @@ struct SmolLm {
     size_t page_elems = 0, slot_floats = 0, esize = 2;
     int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
     // workspace carving (byte offsets)
-    size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_q, o_hw, o_err, total;
+    size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_q, o_hw, o_err, o_part, total;
+    int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
     char* ws = nullptr;
     void* pages = nullptr;
     float* slots = nullptr;
@@ -633,7 +964,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     if (!cfg || !layers || !run_layer || !out) return fail(SMOL_ERR_INVALID, "smol_lm_create: null argument");
     if (cfg->dtype != SMOL_LM_BF16 && cfg->dtype != SMOL_LM_F32) return fail(SMOL_ERR_INVALID, "dtype must be 0 (bf16) or 1 (f32)");
     if (cfg->vocab < 1 || cfg->width < 1 || cfg->n_layers < 1 || cfg->n_runs < 1 || cfg->page_size < 1 || cfg->max_step_tokens < 1 ||
-        cfg->max_step_seqs < 1 || cfg->max_want < 1)
+        cfg->max_step_seqs < 1 || cfg->max_want < 1 || cfg->max_context < 1)
         return fail(SMOL_ERR_INVALID, "smol_lm_create: sizes must be positive");
     SmolLm* m = new SmolLm();
     m->cfg = *cfg;
@@ -653,6 +984,8 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             r.v_off = r.k_off + (size_t)L.kv_heads * cfg->page_size * L.dim;
             m->page_elems = r.v_off + (size_t)L.kv_heads * cfg->page_size * L.vdim;
             m->max_q = std::max(m->max_q, L.heads * L.dim);
+            m->max_heads = std::max(m->max_heads, L.heads);
+            m->max_vdim = std::max(m->max_vdim, L.vdim);
             m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
         } else if (L.mixer == SMOL_LM_MIX_GENERAL_DELTA) {
             if (L.dim > 128) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 128"); }
@@ -688,6 +1021,11 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     m->o_q = carve(T * (size_t)std::max(m->max_q, 1) * E);
     m->o_hw = carve((size_t)cfg->max_want * D * E);
     m->o_err = carve(256);
+    // few-token attention: key ranges of split_len positions, at most 64 of them per row
+    const int ctx = std::max(cfg->max_context, 1);
+    m->split_len = std::max(256, ((ctx + 63) / 64 + 63) / 64 * 64);
+    m->max_splits = (ctx + m->split_len - 1) / m->split_len;
+    m->o_part = carve((size_t)cfg->max_step_seqs * kShortSeq * m->max_heads * m->max_splits * (m->max_vdim + 2) * 4);
     m->total = o;
     *out = m;
     return SMOL_OK;
@@ -737,7 +1075,13 @@ cudaError_t linear<float>(SmolLm* m, const float* a, const float* w, float* y, i
 
 template <>
 cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int M, int N, int K, cudaStream_t st) {
-    if (M <= 32) {
+    if (M <= 8 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
+        const int grid = (N + 7) / 8;
+        if (M == 1) gemv_bf16_kernel<1><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+        else if (M == 2) gemv_bf16_kernel<2><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+        else if (M <= 4) gemv_bf16_kernel<4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+        else gemv_bf16_kernel<8><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+    } else if (M <= 32) {
         dim3 grid((N + 31) / 32, (M + 31) / 32);
         gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 32 x 32
     } else if (M <= 256) {
@@ -754,8 +1098,8 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
 template <int DK, class T>
 static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec, const float* u, const float* au, float* pool, T* out,
                                cudaStream_t st) {
-    const int threads = (A.d + 31) / 32 * 32;
-    const size_t smem = (size_t)(5 * kDeltaChunk * DK + 8 * kDeltaChunk) * sizeof(float);
+    const int threads = (4 * A.d + 31) / 32 * 32;
+    const size_t smem = (size_t)(5 * kDeltaChunk * DK + 16 * kDeltaChunk) * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     delta_scan_kernel<DK, T><<<n_seqs * A.H, threads, smem, st>>>(A, dec, u, au, pool, out);
@@ -803,9 +1147,39 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.n_tokens = Tn; A.err = err;
             const int units = Tn * (L.heads + 2 * L.kv_heads);
             attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
-            const int au = Tn * L.heads;
-            attn_kernel<T><<<(au + kAttnWarps - 1) / kAttnWarps, kAttnWarps * 32, kAttnWarps * L.dim * sizeof(float), st>>>(A, qbuf, pool, mix);
-            m->launches += 2;
+            A.seq_start = s->seq_start;
+            A.split_len = m->split_len;
+            A.short_rows = s->n_seqs * kShortSeq;
+            A.part = reinterpret_cast<float*>(m->ws + m->o_part);
+            const int min_n = s->min_seq_tokens > 0 ? s->min_seq_tokens : 1;
+            const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
+            const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
+            A.n_splits = max_pos / m->split_len + 1;
+            const int hp = std::max(L.dim, L.vdim);
+            const bool flash = sizeof(T) == 2 && hp <= 128;
+            if (max_n > kShortSeq) {
+                if (flash) {
+                    dim3 grid((max_n + 63) / 64, s->n_seqs, L.heads);
+                    const bf16* qb = reinterpret_cast<const bf16*>(qbuf);
+                    const bf16* pl = reinterpret_cast<const bf16*>(pool);
+                    bf16* mx = reinterpret_cast<bf16*>(mix);
+                    if (hp <= 32) attn_flash_kernel<32><<<grid, 128, 0, st>>>(A, qb, pl, mx);
+                    else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, 0, st>>>(A, qb, pl, mx);
+                    else attn_flash_kernel<128><<<grid, 128, 0, st>>>(A, qb, pl, mx);
+                } else {
+                    // every row, also those of short sequences
+                    const int au = Tn * L.heads;
+                    attn_kernel<T><<<(au + kAttnWarps - 1) / kAttnWarps, kAttnWarps * 32, kAttnWarps * L.dim * sizeof(float), st>>>(A, qbuf, pool, mix);
+                }
+                m->launches += 1;
+            }
+            if (min_n <= kShortSeq && (flash || max_n <= kShortSeq)) {
+                dim3 grid(A.short_rows, L.kv_heads, A.n_splits);
+                attn_split_kernel<T><<<grid, 128, 4 * L.dim * sizeof(float), st>>>(A, qbuf, pool);
+                attn_merge_kernel<T><<<(A.short_rows * L.heads + 3) / 4, 128, 0, st>>>(A, mix);
+                m->launches += 2;
+            }
+            m->launches += 1;
             mix_cols = L.heads * L.vdim;
         } else {
             DeltaArgs A;

@@ -148,7 +148,8 @@ class PamasunLM:
         ccfg = _capi_lm.SmolLmConfig(
             dtype=_capi_lm.SMOL_LM_F32 if dt == torch.float32 else _capi_lm.SMOL_LM_BF16, vocab=cfg.vocab, width=cfg.width,
             n_layers=len(cfg.layers), n_runs=len(self.runs), page_size=self.page_size, max_step_tokens=self.max_step_tokens,
-            max_step_seqs=self.max_seqs, max_want=self.max_want, embed_scale=cfg.embedding_scale, norm_eps=cfg.norm_eps)
+            max_step_seqs=self.max_seqs, max_want=self.max_want,
+            max_context=self.page_pool.n * self.page_size, embed_scale=cfg.embedding_scale, norm_eps=cfg.norm_eps)
         runs = (C.c_int32 * len(self.runs))(*self.runs)
         if self._h:
             self.lib.smol_lm_destroy(self._h)
@@ -272,7 +273,8 @@ class PamasunLM:
         base = self._meta_dev.data_ptr()
         tr = torch.empty(len(self.runs), T, self.config.width, dtype=torch.float32, device=self.device) if trace else None
         step = _capi_lm.SmolLmStep(
-            n_tokens=T, n_seqs=S, n_want=n_want, max_pages=P, tokens=base + 4 * o_tok, tok_seq=base + 4 * o_seq,
+            n_tokens=T, n_seqs=S, n_want=n_want, max_pages=P, min_seq_tokens=min(len(t) for _, t, _ in entries),
+            max_seq_tokens=max(len(t) for _, t, _ in entries), max_pos=max(q.length + len(t) for q, t, _ in entries) - 1, tokens=base + 4 * o_tok, tok_seq=base + 4 * o_seq,
             tok_pos=base + 4 * o_pos, seq_start=base + 4 * o_start, seq_pos0=base + 4 * o_pos0, seq_slot=base + 4 * o_slot,
             block_table=base + 4 * o_bt, want_rows=base + 4 * o_want, logits=self._logits.data_ptr(),
             trace=tr.data_ptr() if trace else None)

@@ -1,0 +1,207 @@
+"""Prefill and decode throughput of the hybrid language-model engine at layer sizes that resemble a real model's,
+beside the DualAR slow transformer (the package's closest model: attention + gated MLP layers) at equal size.
+
+``python bench.py --lm`` prints one JSON line: for every size, tokens/s of a whole-prompt prefill and of single-token
+decode steps against a filled cache, each with its distance from the roofline (matrix-product + attention flops over the
+measured bf16 peak for prefill; weight + cache + state bytes over the measured copy bandwidth for decode).  Weights are
+random, inputs synthetic; every timed region is bracketed by CUDA events after warm-up, and the working set of a
+step (the weights) is larger than L2 for the sizes below.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Dict, List
+
+import torch
+
+SIZES = {
+    # name: width, layers, heads, kv_heads, head size, feed-forward, vocab, pattern (d = generalized delta rule, a = attention)
+    "w768": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, ff=4608, vocab=2368, pattern="daa"),
+    "w1536": dict(width=1536, layers=12, heads=12, kv_heads=4, dim=128, ff=6144, vocab=8192, pattern="daa"),
+    "w768attn": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, ff=4608, vocab=2368, pattern="a"),
+}
+
+
+def pamasun_config(width, layers, heads, kv_heads, dim, ff, vocab, pattern) -> dict:
+    ls = []
+    for i in range(layers):
+        if pattern[i % len(pattern)] == "a":
+            ls.append({"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5},
+                       "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            ls.append({"type": "general_delta", "mixer": {"heads": heads, "dim": dim}, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Pamasun", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-5},
+            "layers": ls, "loop": {"start": 0, "stop": 0, "times": 1}}
+
+
+def random_state_dict(cfg, seed: int = 0, rank: int = 64) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    shapes = cfg.tensor_shapes({i: rank for i in range(len(cfg.layers))})
+    sd = {}
+    for k, s in shapes.items():
+        if len(s) == 2:
+            sd[k] = (torch.randn(*s, generator=g) * (s[1] ** -0.5)).bfloat16()
+        elif k.endswith(("ls1", "ls2")):
+            sd[k] = torch.full(s, 0.5).bfloat16()
+        elif k.endswith(("q.norm", "k.norm", "mix.norm")):
+            sd[k] = torch.ones(s).bfloat16()
+        elif k.endswith("act"):
+            sd[k] = torch.tensor([0.6, 0.3, 0.1, 0.0]).bfloat16()
+        elif k.endswith(("r1", "r2")):
+            sd[k] = torch.full(s, 0.5).bfloat16()
+        else:
+            sd[k] = (torch.randn(*s, generator=g) * 0.05).bfloat16()
+    sd["embed"] = (torch.randn(*shapes["embed"], generator=g) * (shapes["embed"][1] ** -0.5)).bfloat16()
+    return sd
+
+
+def _timed(fn, warmup: int, steps: int) -> float:
+    """Mean milliseconds of fn() over `steps` calls, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def _peaks(root: str):
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def bench_pamasun(name: str, prompt: int, batch: int, decode_steps: int, warmup: int, steps: int, peaks) -> dict:
+    from .lm import PamasunLM
+    from .lm_config import PamasunConfig
+
+    hbm, tflops, _ = peaks
+    spec = SIZES[name]
+    cfg = PamasunConfig.from_dict(pamasun_config(**spec))
+    rank = 64
+    model = PamasunLM(cfg, dtype=torch.bfloat16, max_tokens=batch * (prompt + 64 + decode_steps), max_seqs=batch, page_size=64,
+                      max_step_tokens=2048, max_want=batch)
+    model.load_state_dict(random_state_dict(cfg, 0, rank))
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (batch, prompt + decode_steps), generator=g).tolist()
+    n_attn = sum(cfg.layers[i].mixer.kind == "attention" for i in cfg.layer_runs())
+    n_delta = len(cfg.layer_runs()) - n_attn
+    H, d = spec["heads"], spec["dim"]
+    mm_flops = cfg.matmul_flops_per_token(rank) - 2 * cfg.vocab * cfg.width            # the head runs on wanted rows only
+    wbytes = 2 * cfg.weight_elements(rank)
+
+    # ---- prefill: one sequence, the whole prompt, logits of its last token
+    def prefill():
+        seq = model.open_sequence()
+        for lo in range(0, prompt, model.max_step_tokens):
+            part = toks[0][lo:min(prompt, lo + model.max_step_tokens)]
+            model.forward([(seq, part, [len(part) - 1] if lo + len(part) == prompt else [])])
+        model.close_sequence(seq)
+
+    l0 = model.launch_count
+    ms_p = _timed(prefill, warmup, steps)
+    launches = model.launch_count - l0
+    flops_p = prompt * mm_flops + n_attn * 4 * H * d * prompt * (prompt + 1) / 2 + n_delta * 6 * H * d * d * prompt
+    # ---- decode: `batch` sequences with `prompt` cached positions, one token each per step
+    seqs = [model.open_sequence() for _ in range(batch)]
+    for b, s in enumerate(seqs):
+        for lo in range(0, prompt, model.max_step_tokens):
+            model.forward([(s, toks[b][lo:min(prompt, lo + model.max_step_tokens)], [])])
+
+    def decode():
+        for i in range(decode_steps):
+            model.forward([(s, [toks[b][prompt + i]], [0]) for b, s in enumerate(seqs)])
+        for s in seqs:
+            s.length = prompt                                 # the next timed pass decodes against the same context
+
+    l0 = model.launch_count
+    ms_d = _timed(decode, 2, steps) / decode_steps
+    launches += model.launch_count - l0
+    ctx = prompt + decode_steps / 2
+    kv_bytes = n_attn * 2 * spec["kv_heads"] * d * 2 * ctx * batch
+    st_bytes = n_delta * 2 * H * d * d * 4 * batch
+    bytes_d = wbytes + kv_bytes + st_bytes
+    model.check_device_errors()
+    for s in seqs:
+        model.close_sequence(s)
+    return {"model": f"Pamasun {name}", "spec": spec, "parameters_m": round(cfg.weight_elements(rank) / 1e6, 1),
+            "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
+                        "of_peak": flops_p / ms_p / 1e9 / tflops},
+            "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
+                       "gbs": bytes_d / ms_d / 1e6, "of_peak": bytes_d / ms_d / 1e6 / hbm},
+            "gpu_launches": int(launches)}
+
+
+def bench_dualar(prompt: int, batch: int, decode_steps: int, warmup: int, steps: int, peaks) -> dict:
+    """The slow transformer of smoltts_byte_150m (width 768, 10 layers, 12/4 heads of 64, gated MLP 3072): prefill of one
+    prompt and single-position slow steps of `batch` sequences."""
+    from . import RQTransformer, named_config
+    from .synth import make_state_dict
+
+    hbm, tflops, _ = peaks
+    cfg = named_config("smoltts_byte_150m")
+    model = RQTransformer(cfg, max_batch=max(batch, 1), max_seq_len=prompt + decode_steps + 64)
+    model.load_state_dict(make_state_dict(cfg, seed=0))
+    R = cfg.n_rows
+    g = torch.Generator().manual_seed(2)
+    grid = torch.zeros(1, R, prompt + 1, dtype=torch.int32)
+    grid[:, 0] = torch.randint(0, 256, (1, prompt + 1), generator=g).to(torch.int32)
+    d_grid = grid.to(model.device)
+    lens = torch.tensor([prompt + 1], dtype=torch.int32, device=model.device)
+    l0 = model.launch_count
+
+    def prefill():
+        b = model.new_batch(1, max_positions=prompt + 8)
+        model.prefill(b, d_grid, lens)
+        b.release()
+
+    ms_p = _timed(prefill, warmup, steps)
+    slow = cfg.n_layer * cfg.layer_params()
+    flops_p = prompt * 2 * slow + cfg.n_layer * 4 * cfg.n_head * 64 * prompt * (prompt + 1) / 2
+    bb = model.new_batch(batch, max_positions=prompt + decode_steps + 8)
+    gridb = d_grid.expand(batch, R, prompt + 1).contiguous()
+    model.prefill(bb, gridb, lens.expand(batch).contiguous())
+    torch.cuda.synchronize()
+    len0, host0 = bb.seq_len.clone(), list(bb.host_len)
+
+    def decode():
+        for _ in range(decode_steps):
+            model.slow_step(bb, advance=True)
+        bb.seq_len.copy_(len0)
+        bb.host_len[:] = host0
+
+    ms_d = _timed(decode, 2, steps) / decode_steps
+    ctx = prompt + decode_steps / 2
+    bytes_d = 2 * (slow + cfg.vocab_size * cfg.dim) + cfg.kv_bytes_per_position() * ctx * batch
+    return {"model": "DualAR slow transformer smoltts_byte_150m", "parameters_m": round((slow + cfg.vocab_size * cfg.dim) / 1e6, 1),
+            "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
+                        "of_peak": flops_p / ms_p / 1e9 / tflops},
+            "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
+                       "gbs": bytes_d / ms_d / 1e6, "of_peak": bytes_d / ms_d / 1e6 / hbm, "call": "slow_step (one launch per phase)"},
+            "gpu_launches": int(model.launch_count - l0)}
+
+
+def run(args, root: str) -> None:
+    assert torch.cuda.is_available(), "the language-model benchmark needs a CUDA device"
+    peaks = _peaks(root)
+    names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768attn", "w1536"])]
+    t0 = time.time()
+    entries: List[dict] = []
+    for n in names:
+        for batch in (1, 4):
+            entries.append(bench_pamasun(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+    for batch in (1, 4):
+        entries.append(bench_dualar(args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+    print(json.dumps({"metric": "language-model prefill and decode tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
+                      "peaks": {"hbm_gbs": peaks[0], "bf16_tflops": peaks[1], "source": peaks[2]}, "steps": args.steps,
+                      "warmup": args.warmup, "entries": entries, "gpu_launches": sum(e["gpu_launches"] for e in entries),
+                      "seconds": round(time.time() - t0, 1)}), flush=True)

@@ -39,7 +39,9 @@ def peaky(w):
 @pytest.mark.parametrize("layers", [
     [attn(ff=0)], [delta(ff=0)], [attn(heads=1, kv_heads=1, dim=8, vdim=8, ff=40)], [delta(heads=1, dim=32, ff=0, rank=3)],
     [attn(heads=6, kv_heads=2, dim=24, vdim=40, scale=0.2, ff=0)], [delta(heads=2, dim=48, ff=0, rank=16)],
-    [delta(heads=1, dim=128, ff=0)]], ids=["attention", "delta", "mha+mlp", "delta32", "gqa-odd", "delta48", "delta128"])
+    [delta(heads=1, dim=128, ff=0)], [attn(heads=3, kv_heads=1, dim=12, vdim=20, scale=0.3, ff=0)],
+    [attn(heads=2, kv_heads=1, dim=128, vdim=64, scale=0.09, ff=0)], [attn(heads=2, kv_heads=2, dim=40, vdim=136, scale=0.15, ff=0)]],
+    ids=["attention", "delta", "mha+mlp", "delta32", "gqa-odd", "delta48", "delta128", "attn-unaligned", "attn128", "attn-wide-v"])
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
 def test_each_mechanism_alone(layers, dtype):
     cfg = config(layers, vocab=61, width=72)
@@ -65,18 +67,19 @@ def test_every_layer_run_of_a_looped_hybrid(dtype):
     assert rel_err(logits, want) < TOL[dtype]
 
 
-def test_prefill_against_token_by_token_and_portions():
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_prefill_against_token_by_token_and_portions(dtype):
     from smoltts_b200.serving import TokenBatcher
 
-    model, orc, _ = engine_and_oracle(MIXED, seed=3, edit=peaky)
+    model, orc, _ = engine_and_oracle(MIXED, seed=3, edit=peaky, dtype=dtype)
     toks = tokens(90, MIXED["vocab"], 2)
     want = orc.forward(toks)
     whole = run_whole(model, toks)
-    assert rel_err(whole, want) < TOL[F32]
+    assert rel_err(whole, want) < TOL[dtype]
     b = TokenBatcher(model)
     one = torch.cat([b.feed([("d", [t], [0])]) for t in toks])
     b.feed([("d", [0], [])], end=["d"])
-    assert rel_err(one, want) < TOL[F32] and rel_err(one, whole) < 1e-4
+    assert rel_err(one, want) < TOL[dtype] and rel_err(one, whole) < (1e-4 if dtype == F32 else TOL[dtype])
     for sizes in ([2] * 45, [17, 2, 31, 3, 2, 16, 15, 2, 2], [15, 1, 16, 16, 1, 1, 33, 7], [64, 26]):
         assert sum(sizes) == 90
         outs, at = [], 0
@@ -84,22 +87,23 @@ def test_prefill_against_token_by_token_and_portions():
             outs.append(b.feed([("p", toks[at:at + n], list(range(n)))], end=["p"] if at + n == 90 else []))
             at += n
         got = torch.cat(outs)
-        assert rel_err(got, want) < TOL[F32], sizes
-        assert rel_err(got, whole) < 1e-4, sizes
+        assert rel_err(got, want) < TOL[dtype], sizes
+        assert rel_err(got, whole) < (1e-4 if dtype == F32 else TOL[dtype]), sizes
     assert len(model.page_pool) == model.page_pool.n and len(model.slot_pool) == model.slot_pool.n
 
 
-def test_unequal_batches_equal_each_alone_with_reused_pages_and_slots():
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_unequal_batches_equal_each_alone_with_reused_pages_and_slots(dtype):
     """Four requests of different lengths share steps: portions beside single tokens, requests that pause, finish and are
     replaced.  The pool holds fewer pages than all requests together need, so pages and slots are used again, and the
     pools are filled with garbage first: nothing may depend on what a page or slot held before."""
     from smoltts_b200.serving import TokenBatcher
 
-    model, orc, _ = engine_and_oracle(MIXED, seed=4, edit=peaky, max_tokens=208, max_seqs=3)
-    model._kv_pool.view(torch.float32).fill_(1e4)
+    model, orc, _ = engine_and_oracle(MIXED, seed=4, edit=peaky, max_tokens=208, max_seqs=3, dtype=dtype)
+    model._kv_pool.view(dtype).fill_(1e4)
     model._state_pool.view(torch.float32).fill_(-3e3)
     V = MIXED["vocab"]
-    reqs = {"a": tokens(70, V, 10), "b": tokens(33, V, 11), "c": tokens(5, V, 12), "d": tokens(64, V, 13), "e": tokens(49, V, 14)}
+    reqs = {"a": tokens(70, V, 10), "b": tokens(33, V, 11), "c": tokens(5, V, 12), "d": tokens(64, V, 13), "e": tokens(49, V, 17)}
     want = {k: orc.forward(v) for k, v in reqs.items()}
     plan = [[("a", 16), ("b", 2), ("c", 1)], [("a", 3), ("b", 29), ("c", 4)], [("a", 13), ("b", 1), ("d", 2)],
             [("a", 1), ("b", 1), ("d", 30)], [("a", 1), ("d", 1)], [("a", 33), ("d", 31), ("e", 17)], [("a", 1), ("e", 2)],
@@ -120,7 +124,7 @@ def test_unequal_batches_equal_each_alone_with_reused_pages_and_slots():
     model.check_device_errors()
     assert at == {k: len(v) for k, v in reqs.items()}
     for k in reqs:
-        assert rel_err(torch.cat(got[k]), want[k]) < TOL[F32], k
+        assert rel_err(torch.cat(got[k]), want[k]) < TOL[dtype], k
     assert len(model.page_pool) == model.page_pool.n and len(model.slot_pool) == 3
 
 

@@ -51,7 +51,7 @@ typedef struct SmolLmLayer {
     const float *q_norm, *k_norm;                   /* attention: plain RMS-norm weights [dim] */
     const float *dist_r1, *dist_r2, *sink;          /* attention: distance penalty r1 ln(1 + r2 (i - j)) and sink logit, [heads] */
     const float *rate_bias;                         /* recurrent: [heads * dim] */
-    const float *decay_w2, *decay_bias;             /* recurrent: [heads * dim, rank] fp32, [heads * dim] */
+    const float *decay_w2, *decay_bias;             /* recurrent: second decay matrix TRANSPOSED, [rank, heads * dim] fp32; [heads * dim] */
     const float *out_norm;                          /* recurrent: plain weight after the per-head RMS division [heads * dim] */
     const float *act;                               /* PolyNorm coefficients a, b, c, e */
 } SmolLmLayer;

@@ -460,9 +460,43 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
 // positions, so a row's result does not depend on what else is in the step.
 constexpr int kShortSeq = 8;          // a sequence with at most this many tokens in a step takes this path
 
+// q (fp32, shared memory) . k (one cached key row), 16-byte loads where the row allows them
+template <class T> __device__ __forceinline__ float key_dot(const float* qs, const T* k, int d);
+template <> __device__ __forceinline__ float key_dot<float>(const float* qs, const float* k, int d) {
+    float dot = 0.0f;
+    if (d % 4 == 0 && reinterpret_cast<uintptr_t>(k) % 16 == 0) {
+        for (int c = 0; c < d; c += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(k + c);
+            dot = fmaf(qs[c], v.x, dot); dot = fmaf(qs[c + 1], v.y, dot); dot = fmaf(qs[c + 2], v.z, dot); dot = fmaf(qs[c + 3], v.w, dot);
+        }
+    } else {
+        for (int c = 0; c < d; ++c) dot = fmaf(qs[c], k[c], dot);
+    }
+    return dot;
+}
+template <> __device__ __forceinline__ float key_dot<bf16>(const float* qs, const bf16* k, int d) {
+    float dot = 0.0f;
+    if (d % 8 == 0 && reinterpret_cast<uintptr_t>(k) % 16 == 0) {
+        for (int c = 0; c < d; c += 8) {
+            const uint4 v = ldg_v4(k + c);
+            dot = fmaf(qs[c], bf_lo(v.x), dot); dot = fmaf(qs[c + 1], bf_hi(v.x), dot);
+            dot = fmaf(qs[c + 2], bf_lo(v.y), dot); dot = fmaf(qs[c + 3], bf_hi(v.y), dot);
+            dot = fmaf(qs[c + 4], bf_lo(v.z), dot); dot = fmaf(qs[c + 5], bf_hi(v.z), dot);
+            dot = fmaf(qs[c + 6], bf_lo(v.w), dot); dot = fmaf(qs[c + 7], bf_hi(v.w), dot);
+        }
+    } else {
+        for (int c = 0; c < d; ++c) dot = fmaf(qs[c], __bfloat162float(k[c]), dot);
+    }
+    return dot;
+}
+
 template <class T>
-__global__ void __launch_bounds__(128) attn_split_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool) {
-    extern __shared__ float qs_all[];
+__global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool) {
+    // One block per (row, key/value head x group of up to 8 of its query heads, key range); one warp per query head.
+    // 32 keys and values at a time are staged in shared memory (rows padded by 16 bytes: conflict-free row-per-lane
+    // reads), so that no global load sits inside the softmax / value loops.
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    constexpr int kPad = 16 / (int)sizeof(T);
     const int s = blockIdx.x / kShortSeq, r = blockIdx.x % kShortSeq;
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
     if (n > kShortSeq || r >= n) return;
@@ -470,58 +504,76 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const AttnArgs A, const
     const int j_lo = blockIdx.z * A.split_len;
     if (j_lo > pos) return;
     const int j_hi = min(pos, j_lo + A.split_len - 1);
-    const int g = blockIdx.y, Gq = A.H / A.G;
+    const int Gq = A.H / A.G, nwarp = blockDim.x >> 5;
+    const int groups = (Gq + nwarp - 1) / nwarp;
+    const int g = blockIdx.y / groups, hq = (blockIdx.y % groups) * nwarp + (threadIdx.x >> 5);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool active = hq < Gq;
+    const int h = g * Gq + (active ? hq : 0);
+    const int ldk = A.d + kPad, ldv = A.dv + kPad;
+    float* qs = reinterpret_cast<float*>(sm_raw) + warp * A.d;
+    float* ps = reinterpret_cast<float*>(sm_raw) + nwarp * A.d + warp * 32;
+    T* Ks = reinterpret_cast<T*>(sm_raw + (((size_t)nwarp * (A.d + 32) * 4 + 15) / 16) * 16);
+    T* Vs = Ks + 32 * ldk;
     const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
-    float* qs = qs_all + warp * A.d;
-    for (int hq = warp; hq < Gq; hq += 4) {
-        const int h = g * Gq + hq;
-        __syncwarp();
-        for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
-        __syncwarp();
-        const float r1 = A.r1[h], r2 = A.r2[h];
-        float m = -INFINITY, l = 0.0f;
-        float o[kAttnMaxV];
+    for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
+    const float r1 = A.r1[h], r2 = A.r2[h];
+    float m = -INFINITY, l = 0.0f;
+    float o[kAttnMaxV];
 #pragma unroll
-        for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
-        for (int j0 = j_lo; j0 <= j_hi; j0 += 32) {
-            const int j = j0 + lane;
-            float sc = -INFINITY;
-            const T* vrow = nullptr;
-            if (j <= j_hi) {
-                const int page = bt[j / A.page_size], in_pg = j % A.page_size;
-                const T* base = pool + (size_t)page * A.page_elems;
-                const T* k = base + A.k_off + ((size_t)g * A.page_size + in_pg) * A.d;
-                vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv;
-                float dot = 0.0f;
-                for (int c = 0; c < A.d; ++c) dot = fmaf(qs[c], to_f<T>(k[c]), dot);
-                sc = dot * A.scale - r1 * log1pf(r2 * (float)(pos - j));
-            }
-            const float mn = fmaxf(m, warp_max(sc));          // finite: lane 0 of every round holds a valid key
-            const float p = (j <= j_hi) ? expf(sc - mn) : 0.0f;
-            const float corr = expf(m - mn);
-            l = l * corr + warp_sum(p);
-            m = mn;
-#pragma unroll
-            for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
-            const int cnt = min(32, j_hi - j0 + 1);
-            for (int jj = 0; jj < cnt; ++jj) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
-                const T* vr = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(vrow), jj));
-#pragma unroll
-                for (int e = 0; e < kAttnMaxV; ++e) {
-                    const int c = lane + e * 32;
-                    if (c < A.dv) o[e] = fmaf(pj, to_f<T>(vr[c]), o[e]);
-                }
+    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+    const bool kvec = (A.d * sizeof(T)) % 16 == 0, vvec = (A.dv * sizeof(T)) % 16 == 0;
+    const int kchunks = kvec ? A.d / kPad : A.d, vchunks = vvec ? A.dv / kPad : A.dv;
+    for (int j0 = j_lo; j0 <= j_hi; j0 += 32) {
+        const int cnt = min(32, j_hi - j0 + 1);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < cnt * (kchunks + vchunks); idx += blockDim.x) {
+            const int row = idx / (kchunks + vchunks), c = idx % (kchunks + vchunks);
+            const int j = j0 + row;
+            const T* base = pool + (size_t)bt[j / A.page_size] * A.page_elems;
+            const size_t in_pg = (size_t)g * A.page_size + j % A.page_size;
+            if (c < kchunks) {
+                const T* src = base + A.k_off + in_pg * A.d;
+                if (kvec) *reinterpret_cast<uint4*>(Ks + row * ldk + c * kPad) = *reinterpret_cast<const uint4*>(src + c * kPad);
+                else Ks[row * ldk + c] = src[c];
+            } else {
+                const int cv = c - kchunks;
+                const T* src = base + A.v_off + in_pg * A.dv;
+                if (vvec) *reinterpret_cast<uint4*>(Vs + row * ldv + cv * kPad) = *reinterpret_cast<const uint4*>(src + cv * kPad);
+                else Vs[row * ldv + cv] = src[cv];
             }
         }
-        float* dst = A.part + (((size_t)blockIdx.x * A.H + h) * A.n_splits + blockIdx.z) * (A.dv + 2);
-        if (lane == 0) { dst[0] = m; dst[1] = l; }
+        __syncthreads();
+        if (!active) continue;
+        const int j = j0 + lane;
+        float sc = -INFINITY;
+        if (lane < cnt) sc = key_dot<T>(qs, Ks + lane * ldk, A.d) * A.scale - r1 * log1pf(r2 * (float)(pos - j));
+        const float mn = fmaxf(m, warp_max(sc));          // finite: lane 0 of every round holds a valid key
+        const float p = lane < cnt ? expf(sc - mn) : 0.0f;
+        const float corr = expf(m - mn);
+        l = l * corr + warp_sum(p);
+        m = mn;
+        ps[lane] = p;
+        __syncwarp();
 #pragma unroll
-        for (int e = 0; e < kAttnMaxV; ++e) {
-            const int c = lane + e * 32;
-            if (c < A.dv) dst[2 + c] = o[e];
+        for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = ps[jj];
+#pragma unroll
+            for (int e = 0; e < kAttnMaxV; ++e) {
+                const int c = lane + e * 32;
+                if (c < A.dv) o[e] = fmaf(pj, to_f<T>(Vs[jj * ldv + c]), o[e]);
+            }
         }
+        __syncwarp();
+    }
+    if (!active) return;
+    float* dst = A.part + (((size_t)blockIdx.x * A.H + h) * A.n_splits + blockIdx.z) * (A.dv + 2);
+    if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int e = 0; e < kAttnMaxV; ++e) {
+        const int c = lane + e * 32;
+        if (c < A.dv) dst[2 + c] = o[e];
     }
 }
 
@@ -742,7 +794,7 @@ struct DeltaArgs {
 // Per token and channel: decay w = exp(-coef * sigmoid(w2 tanh(inner) + bias)), unit key u, removal vector a * u.
 __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, float* __restrict__ ukey, float* __restrict__ aukey) {
     extern __shared__ float th[];   // tanh(inner) [rank], then per-head 1/|k|
-    const int t = blockIdx.x, HD = A.H * A.d;
+    const int t = blockIdx.x, HD = A.H * A.d;      // blockIdx.y: a slice of blockDim.x channels
     const float* row = A.proj + (size_t)t * A.n_in;
     float* inv = th + A.rank;
     for (int r = threadIdx.x; r < A.rank; r += blockDim.x) th[r] = tanhf(row[5 * HD + r]);
@@ -755,10 +807,10 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
         if (lane == 0) inv[h] = 1.0f / sqrtf(ss + A.unit_eps);
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < HD; c += gridDim.y * blockDim.x) {
         float lo = A.decay_bias[c];
-        const float* w2 = A.decay_w2 + (size_t)c * A.rank;
-        for (int r = 0; r < A.rank; ++r) lo = fmaf(w2[r], th[r], lo);
+#pragma unroll 8
+        for (int r = 0; r < A.rank; ++r) lo = fmaf(A.decay_w2[(size_t)r * HD + c], th[r], lo);
         const float u = row[HD + c] * inv[c / A.d];
         const float a = sigmoidf_(row[4 * HD + c] + A.rate_bias[c]);
         decay[(size_t)t * HD + c] = expf(-A.decay_coef * sigmoidf_(lo));
@@ -767,29 +819,58 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
     }
 }
 
-// The recurrence.  One block per (sequence, head).  Four adjacent lanes share value column j of the state: lane q of
-// the four keeps rows q*R .. q*R+R-1 (R = DK / 4, DK >= d key channels; channels beyond d are padded with zero keys) in
-// registers, and the two sums over key channels are finished with two shuffles each.  Tokens are staged through shared
-// memory kDeltaChunk at a time.  Per token:  seen = sum_i u_i S_i;  S_i <- w_i S_i - (a u)_i seen + k_i v_j;
-// o_j = sum_i S_i r_i.  The epilogue divides each head's o by its root mean square, applies the plain weight and the
-// sigmoid gate, and writes the mixer's output in T.
+// The recurrence.  One block per (sequence, head).  Four adjacent lanes share a group of C value columns of the state:
+// lane q of the four keeps rows q*R .. q*R+R-1 (R = DK / 4, DK >= d key channels; channels beyond d are padded with
+// zero keys) of those columns in registers, and the two sums over key channels are finished with two shuffles each.
+// Per token and column j:
+//   seen = sum_i u_i S_ij;   S_ij <- w_i S_ij - (a u)_i seen + k_i v_j;   o_j = sum_i S_ij r_i.
+// Everything a token needs (r, k, u, a u, w over the key channels; v and the gate over the columns) is brought into
+// shared memory kDeltaChunk tokens at a time with cp.async, the next chunk while the current one is computed, so the
+// token loop reads no global memory; a thread's loads of the key-channel vectors serve its C columns, which keeps the
+// loop off the shared-memory bandwidth limit.  The epilogue divides each head's o by its root mean square, applies
+// the plain weight and the sigmoid gate, and writes the mixer's output in T.
 constexpr int kDeltaChunk = 16;
+constexpr int kDeltaArrays = 7;   // r, k, u, au, w, v, gate
+
+__host__ __device__ constexpr int delta_cols(int DK) { return DK == 16 ? 1 : (DK == 64 ? 4 : 2); }
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+template <int DK>
+__device__ __forceinline__ void delta_stage(const DeltaArgs& A, float* buf, int c0, int n, int h, const float* decay, const float* ukey,
+                                            const float* aukey) {
+    const int d = A.d, HD = A.H * d;
+    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
+        const int tt = idx / d, i = idx % d;
+        const float* prow = A.proj + (size_t)(c0 + tt) * A.n_in + h * d + i;
+        const size_t vrow = (size_t)(c0 + tt) * HD + h * d + i;
+        float* dst = buf + tt * DK + i;
+        cp_async4(dst, prow);                                       // r
+        cp_async4(dst + kDeltaChunk * DK, prow + HD);               // k
+        cp_async4(dst + 2 * kDeltaChunk * DK, ukey + vrow);
+        cp_async4(dst + 3 * kDeltaChunk * DK, aukey + vrow);
+        cp_async4(dst + 4 * kDeltaChunk * DK, decay + vrow);
+        cp_async4(dst + 5 * kDeltaChunk * DK, prow + 2 * HD);       // v
+        cp_async4(dst + 6 * kDeltaChunk * DK, prow + 3 * HD);       // gate
+    }
+}
 
 template <int DK, class T>
-__global__ void __launch_bounds__(DK * 4) delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay, const float* __restrict__ ukey,
-                                                           const float* __restrict__ aukey, float* __restrict__ state_pool, T* __restrict__ out) {
-    constexpr int R = DK / 4;
+__global__ void __launch_bounds__(DK * 4 / delta_cols(DK)) delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay,
+                                                                            const float* __restrict__ ukey, const float* __restrict__ aukey,
+                                                                            float* __restrict__ state_pool, T* __restrict__ out) {
+    constexpr int C = delta_cols(DK), R = DK / 4;
+    constexpr int kBuf = kDeltaArrays * kDeltaChunk * DK;
     extern __shared__ __align__(16) float sh[];
+    float* s_o = sh + 2 * kBuf;                  // [chunk][DK]
     const int d = A.d, HD = A.H * d;
-    float* s_r = sh;                             // [chunk][DK] each
-    float* s_k = s_r + kDeltaChunk * DK;
-    float* s_u = s_k + kDeltaChunk * DK;
-    float* s_au = s_u + kDeltaChunk * DK;
-    float* s_w = s_au + kDeltaChunk * DK;
-    float* s_red = s_w + kDeltaChunk * DK;       // [warps][chunk]
     const int seq = blockIdx.x / A.H, h = blockIdx.x % A.H;
-    const int j = threadIdx.x >> 2, q = threadIdx.x & 3;
-    const bool live = j < d;
+    const int jc = (threadIdx.x >> 2) * C, q = threadIdx.x & 3;
     const int nw = (blockDim.x + 31) >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = A.seq_start[seq], t1 = A.seq_start[seq + 1];
     const int slot = A.seq_slot[seq];
@@ -797,94 +878,113 @@ __global__ void __launch_bounds__(DK * 4) delta_scan_kernel(const DeltaArgs A, c
         if (threadIdx.x == 0) atomicExch(A.err, 2);
         return;
     }
+    for (int i = threadIdx.x; i < 2 * kBuf; i += blockDim.x) sh[i] = 0.0f;      // padded channels and columns stay zero for good
+    __syncthreads();
+    delta_stage<DK>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, decay, ukey, aukey);
+    cp_async_commit();
     float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * d;
-    float S[R];
+    float S[C][R];
     const bool fresh = A.seq_pos0[seq] == 0;
 #pragma unroll
-    for (int e = 0; e < R; ++e) {
-        const int i = q * R + e;
-        S[e] = (live && !fresh && i < d) ? st[(size_t)i * d + j] : 0.0f;
-    }
-    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
+    for (int cc = 0; cc < C; ++cc)
+#pragma unroll
+        for (int e = 0; e < R; ++e) {
+            const int i = q * R + e, j = jc + cc;
+            S[cc][e] = (!fresh && i < d && j < d && jc < DK) ? st[(size_t)i * d + j] : 0.0f;
+        }
+    const bool own = jc < DK;                    // threads past the padded width only help with staging and the epilogue
+    int cur = 0;
+    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk, cur ^= 1) {
         const int n = min(kDeltaChunk, t1 - c0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < n * DK; idx += blockDim.x) {
-            const int tt = idx / DK, i = idx % DK;
-            const size_t prow = (size_t)(c0 + tt) * A.n_in, vrow = (size_t)(c0 + tt) * HD + h * d + i;
-            const bool in = i < d;
-            s_r[idx] = in ? A.proj[prow + h * d + i] : 0.0f;
-            s_k[idx] = in ? A.proj[prow + HD + h * d + i] : 0.0f;
-            s_u[idx] = in ? ukey[vrow] : 0.0f;
-            s_au[idx] = in ? aukey[vrow] : 0.0f;
-            s_w[idx] = in ? decay[vrow] : 0.0f;
+        if (c0 + kDeltaChunk < t1) {
+            delta_stage<DK>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, min(kDeltaChunk, t1 - c0 - kDeltaChunk), h, decay, ukey, aukey);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
-        float o[kDeltaChunk];
-#pragma unroll
-        for (int tt = 0; tt < kDeltaChunk; ++tt) {
-            o[tt] = 0.0f;
-            if (tt < n) {
-                const float v = live ? A.proj[(size_t)(c0 + tt) * A.n_in + 2 * HD + h * d + j] : 0.0f;
+        const float* b = sh + cur * kBuf;
+        const float *s_r = b, *s_k = b + kDeltaChunk * DK, *s_u = b + 2 * kDeltaChunk * DK, *s_au = b + 3 * kDeltaChunk * DK,
+                    *s_w = b + 4 * kDeltaChunk * DK, *s_v = b + 5 * kDeltaChunk * DK, *s_g = b + 6 * kDeltaChunk * DK;
+        if (own) {
+            for (int tt = 0; tt < n; ++tt) {
                 const int base = tt * DK + q * R;
-                float seen = 0.0f;
+                float v[C], sa[C], sb[C];
+#pragma unroll
+                for (int cc = 0; cc < C; ++cc) {
+                    v[cc] = s_v[tt * DK + jc + cc];
+                    sa[cc] = 0.0f;
+                    sb[cc] = 0.0f;
+                }
 #pragma unroll
                 for (int e = 0; e < R; e += 4) {
                     const float4 u4 = *reinterpret_cast<const float4*>(s_u + base + e);
-                    seen = fmaf(u4.x, S[e], seen);
-                    seen = fmaf(u4.y, S[e + 1], seen);
-                    seen = fmaf(u4.z, S[e + 2], seen);
-                    seen = fmaf(u4.w, S[e + 3], seen);
+#pragma unroll
+                    for (int cc = 0; cc < C; ++cc) {
+                        sa[cc] = fmaf(u4.x, S[cc][e], sa[cc]);
+                        sb[cc] = fmaf(u4.y, S[cc][e + 1], sb[cc]);
+                        sa[cc] = fmaf(u4.z, S[cc][e + 2], sa[cc]);
+                        sb[cc] = fmaf(u4.w, S[cc][e + 3], sb[cc]);
+                    }
                 }
-                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
-                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
-                float acc = 0.0f;
+                float seen[C];
+#pragma unroll
+                for (int cc = 0; cc < C; ++cc) {
+                    float t = sa[cc] + sb[cc];
+                    t += __shfl_xor_sync(0xffffffffu, t, 1);
+                    t += __shfl_xor_sync(0xffffffffu, t, 2);
+                    seen[cc] = t;
+                    sa[cc] = 0.0f;
+                    sb[cc] = 0.0f;
+                }
 #pragma unroll
                 for (int e = 0; e < R; e += 4) {
                     const float4 w4 = *reinterpret_cast<const float4*>(s_w + base + e);
                     const float4 a4 = *reinterpret_cast<const float4*>(s_au + base + e);
                     const float4 k4 = *reinterpret_cast<const float4*>(s_k + base + e);
                     const float4 r4 = *reinterpret_cast<const float4*>(s_r + base + e);
-                    S[e] = fmaf(k4.x, v, fmaf(w4.x, S[e], -a4.x * seen));
-                    S[e + 1] = fmaf(k4.y, v, fmaf(w4.y, S[e + 1], -a4.y * seen));
-                    S[e + 2] = fmaf(k4.z, v, fmaf(w4.z, S[e + 2], -a4.z * seen));
-                    S[e + 3] = fmaf(k4.w, v, fmaf(w4.w, S[e + 3], -a4.w * seen));
-                    acc = fmaf(S[e], r4.x, acc);
-                    acc = fmaf(S[e + 1], r4.y, acc);
-                    acc = fmaf(S[e + 2], r4.z, acc);
-                    acc = fmaf(S[e + 3], r4.w, acc);
-                }
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                o[tt] = acc;
-            }
-        }
-        // per-head mean of o^2 for every token of the chunk (each column counted once: by its lane 0)
 #pragma unroll
-        for (int tt = 0; tt < kDeltaChunk; ++tt) {
-            const float sq = warp_sum((live && q == 0) ? o[tt] * o[tt] : 0.0f);
-            if (lane == 0) s_red[warp * kDeltaChunk + tt] = sq;
+                    for (int cc = 0; cc < C; ++cc) {
+                        S[cc][e] = fmaf(k4.x, v[cc], fmaf(w4.x, S[cc][e], -a4.x * seen[cc]));
+                        S[cc][e + 1] = fmaf(k4.y, v[cc], fmaf(w4.y, S[cc][e + 1], -a4.y * seen[cc]));
+                        S[cc][e + 2] = fmaf(k4.z, v[cc], fmaf(w4.z, S[cc][e + 2], -a4.z * seen[cc]));
+                        S[cc][e + 3] = fmaf(k4.w, v[cc], fmaf(w4.w, S[cc][e + 3], -a4.w * seen[cc]));
+                        sa[cc] = fmaf(S[cc][e], r4.x, sa[cc]);
+                        sb[cc] = fmaf(S[cc][e + 1], r4.y, sb[cc]);
+                        sa[cc] = fmaf(S[cc][e + 2], r4.z, sa[cc]);
+                        sb[cc] = fmaf(S[cc][e + 3], r4.w, sb[cc]);
+                    }
+                }
+#pragma unroll
+                for (int cc = 0; cc < C; ++cc) {
+                    float t = sa[cc] + sb[cc];
+                    t += __shfl_xor_sync(0xffffffffu, t, 1);
+                    t += __shfl_xor_sync(0xffffffffu, t, 2);
+                    if (q == 0) s_o[tt * DK + jc + cc] = t;
+                }
+            }
         }
         __syncthreads();
-        if (live && q == 0) {
-            const float nwgt = A.out_norm[h * d + j];
-#pragma unroll
-            for (int tt = 0; tt < kDeltaChunk; ++tt) {
-                if (tt < n) {
-                    float ss = 0.0f;
-                    for (int w = 0; w < nw; ++w) ss += s_red[w * kDeltaChunk + tt];
-                    const float gate = A.proj[(size_t)(c0 + tt) * A.n_in + 3 * HD + h * d + j];
-                    out[(size_t)(c0 + tt) * HD + h * d + j] =
-                        from_f<T>(o[tt] / sqrtf(ss / (float)d + A.eps) * nwgt * sigmoidf_(gate));
-                }
-            }
+        // per-head root mean square of o, output weight and gate: one warp per token
+        for (int tt = warp; tt < n; tt += nw) {
+            float ss = 0.0f;
+            for (int c = lane; c < d; c += 32) ss = fmaf(s_o[tt * DK + c], s_o[tt * DK + c], ss);
+            ss = warp_sum(ss);
+            const float rs = 1.0f / sqrtf(ss / (float)d + A.eps);
+            for (int c = lane; c < d; c += 32)
+                out[(size_t)(c0 + tt) * HD + h * d + c] = from_f<T>(s_o[tt * DK + c] * rs * A.out_norm[h * d + c] * sigmoidf_(s_g[tt * DK + c]));
         }
+        __syncthreads();          // the buffer is refilled two chunks on; s_o is rewritten next chunk
     }
-    if (live) {
+    if (own) {
 #pragma unroll
-        for (int e = 0; e < R; ++e) {
-            const int i = q * R + e;
-            if (i < d) st[(size_t)i * d + j] = S[e];
-        }
+        for (int cc = 0; cc < C; ++cc)
+#pragma unroll
+            for (int e = 0; e < R; ++e) {
+                const int i = q * R + e, j = jc + cc;
+                if (i < d && j < d) st[(size_t)i * d + j] = S[cc][e];
+            }
     }
 }
 
@@ -1098,8 +1198,8 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
 template <int DK, class T>
 static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec, const float* u, const float* au, float* pool, T* out,
                                cudaStream_t st) {
-    const int threads = (4 * A.d + 31) / 32 * 32;
-    const size_t smem = (size_t)(5 * kDeltaChunk * DK + 16 * kDeltaChunk) * sizeof(float);
+    const int threads = std::max(32, DK * 4 / delta_cols(DK));
+    const size_t smem = (size_t)(2 * kDeltaArrays * kDeltaChunk * DK + kDeltaChunk * DK) * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     delta_scan_kernel<DK, T><<<n_seqs * A.H, threads, smem, st>>>(A, dec, u, au, pool, out);
@@ -1174,8 +1274,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 m->launches += 1;
             }
             if (min_n <= kShortSeq && (flash || max_n <= kShortSeq)) {
-                dim3 grid(A.short_rows, L.kv_heads, A.n_splits);
-                attn_split_kernel<T><<<grid, 128, 4 * L.dim * sizeof(float), st>>>(A, qbuf, pool);
+                const int Gq = L.heads / L.kv_heads, nwarp = std::min(Gq, 8), groups = (Gq + nwarp - 1) / nwarp;
+                const int pad = 16 / (int)sizeof(T);
+                const size_t smem = ((size_t)nwarp * (L.dim + 32) * 4 + 15) / 16 * 16 + (size_t)32 * (L.dim + L.vdim + 2 * pad) * sizeof(T);
+                CU(cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+                dim3 grid(A.short_rows, L.kv_heads * groups, A.n_splits);
+                attn_split_kernel<T><<<grid, nwarp * 32, smem, st>>>(A, qbuf, pool);
                 attn_merge_kernel<T><<<(A.short_rows * L.heads + 3) / 4, 128, 0, st>>>(A, mix);
                 m->launches += 2;
             }
@@ -1188,7 +1292,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.rate_bias = L.rate_bias; A.decay_w2 = L.decay_w2; A.decay_bias = L.decay_bias; A.out_norm = L.out_norm;
             A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
             A.slot_floats = m->slot_floats; A.state_off = R.state_off; A.n_slots = m->n_slots; A.err = err;
-            delta_prep_kernel<<<Tn, 128, (L.rank + L.heads) * sizeof(float), st>>>(A, dec, uk, auk);
+            delta_prep_kernel<<<dim3(Tn, (L.heads * L.dim + 127) / 128), 128, (L.rank + L.heads) * sizeof(float), st>>>(A, dec, uk, auk);
             cudaError_t e;
             if (L.dim <= 16) e = launch_scan<16, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
             else if (L.dim <= 32) e = launch_scan<32, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);

@@ -137,7 +137,9 @@ class PamasunLM:
             else:
                 c.rank = rank_of[i]
                 c.w_in = mat(p + "mix.r", p + "mix.k", p + "mix.v", p + "mix.g", p + "mix.a", p + "mix.w1").data_ptr()
-                c.rate_bias, c.decay_w2 = vec(p + "mix.a.b").data_ptr(), vec(p + "mix.w2").data_ptr()
+                w2t = sd[p + "mix.w2"].to(device=dev, dtype=torch.float32).t().contiguous()      # [rank, heads * dim]: coalesced per channel
+                self._keep.append(w2t)
+                c.rate_bias, c.decay_w2 = vec(p + "mix.a.b").data_ptr(), w2t.data_ptr()
                 c.decay_bias, c.out_norm = vec(p + "mix.w0").data_ptr(), vec(p + "mix.norm").data_ptr()
             c.w_out = mat(p + "mix.o").data_ptr()
             if L.mlp_kind:

@@ -66,6 +66,7 @@ typedef struct SmolLmConfig {
     int32_t max_step_seqs;    /* most sequences in one step */
     int32_t max_want;         /* most logits rows asked for in one step */
     int32_t max_context;      /* most positions one sequence may hold (sizes the scratch of the few-token attention path) */
+    int32_t use_graph;        /* 1: steps of few tokens (decoding) are captured once per shape into a CUDA graph and replayed */
     float embed_scale, norm_eps;
 } SmolLmConfig;
 

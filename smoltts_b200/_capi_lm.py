@@ -25,7 +25,7 @@ class SmolLmLayer(C.Structure):
 
 class SmolLmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
-                                         "max_step_seqs", "max_want", "max_context")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
+                                         "max_step_seqs", "max_want", "max_context", "use_graph")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
 
 
 class SmolLmGlobals(C.Structure):

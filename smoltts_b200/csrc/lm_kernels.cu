@@ -458,6 +458,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
 // ranges of A.split_len positions, one block per (row, key/value head, range), whose warps take the query heads of
 // that key/value head; a second kernel merges the ranges with the sink and applies the gate.  The ranges are absolute
 // positions, so a row's result does not depend on what else is in the step.
+constexpr int kGraphMaxTokens = 64;   // steps of at most this many tokens are replayed from a captured graph
 constexpr int kShortSeq = 8;          // a sequence with at most this many tokens in a step takes this path
 
 // q (fp32, shared memory) . k (one cached key row), 16-byte loads where the row allows them
@@ -832,7 +833,7 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
 constexpr int kDeltaChunk = 16;
 constexpr int kDeltaArrays = 7;   // r, k, u, au, w, v, gate
 
-__host__ __device__ constexpr int delta_cols(int DK) { return DK == 16 ? 1 : (DK == 64 ? 4 : 2); }
+__host__ __device__ constexpr int delta_cols(int DK) { return DK == 16 ? 1 : 2; }
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
@@ -1048,6 +1049,14 @@ struct SmolLm {
     int n_pages = 0, n_slots = 0;
     bool bound = false;
     int64_t launches = 0;
+    // small steps (decoding) are captured once per shape into a CUDA graph and replayed
+    struct Captured { SmolLmStep key; cudaGraphExec_t exec; int64_t launches; };
+    std::vector<Captured> graphs;
+    cudaStream_t cap_stream = nullptr;
+    ~SmolLm() {
+        for (auto& g : graphs) cudaGraphExecDestroy(g.exec);
+        if (cap_stream) cudaStreamDestroy(cap_stream);
+    }
 };
 
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
@@ -1138,6 +1147,21 @@ extern "C" size_t smol_lm_workspace_bytes(const SmolLm* m) { return m ? m->total
 extern "C" int64_t smol_lm_launch_count(const SmolLm* m) { return m ? m->launches : 0; }
 extern "C" int32_t* smol_lm_error_word(SmolLm* m) { return (m && m->bound) ? reinterpret_cast<int32_t*>(m->ws + m->o_err) : nullptr; }
 
+template <int DK, class T>
+static cudaError_t scan_attribute() {
+    return cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)((2 * kDeltaArrays * kDeltaChunk * DK + kDeltaChunk * DK) * sizeof(float)));
+}
+template <class T>
+static cudaError_t set_kernel_attributes() {
+    cudaError_t e = scan_attribute<16, T>();
+    if (e == cudaSuccess) e = scan_attribute<32, T>();
+    if (e == cudaSuccess) e = scan_attribute<64, T>();
+    if (e == cudaSuccess) e = scan_attribute<128, T>();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    return e;
+}
+
 extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace, size_t workspace_bytes, void* d_pages, int32_t n_pages,
                             void* d_slots, int32_t n_slots) {
     if (!m || !g || !d_workspace || !d_pages || !d_slots) return fail(SMOL_ERR_INVALID, "smol_lm_bind: null argument");
@@ -1146,6 +1170,8 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
         return fail(SMOL_ERR_INVALID, "smol_lm_bind: workspace must be 256-byte aligned, pages 16-byte aligned");
     if (n_pages < 1 || n_slots < 1) return fail(SMOL_ERR_INVALID, "smol_lm_bind: need at least one page and one slot");
     if (!g->embed || !g->head || !g->final_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: missing global weights");
+    CU(set_kernel_attributes<float>());
+    CU(set_kernel_attributes<bf16>());
     m->g = *g;
     m->ws = static_cast<char*>(d_workspace);
     m->pages = d_pages;
@@ -1184,7 +1210,7 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
     } else if (M <= 32) {
         dim3 grid((N + 31) / 32, (M + 31) / 32);
         gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 32 x 32
-    } else if (M <= 256) {
+    } else if (M <= 256 || ((N + 63) / 64) * ((M + 127) / 128) < 2 * 148) {      // 128-row tiles only when they still fill the GPU twice
         dim3 grid((N + 63) / 64, (M + 63) / 64);
         gemm_bf16_kernel<2, 2, 2, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 64 x 64
     } else {
@@ -1200,8 +1226,6 @@ static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec,
                                cudaStream_t st) {
     const int threads = std::max(32, DK * 4 / delta_cols(DK));
     const size_t smem = (size_t)(2 * kDeltaArrays * kDeltaChunk * DK + kDeltaChunk * DK) * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
     delta_scan_kernel<DK, T><<<n_seqs * A.H, threads, smem, st>>>(A, dec, u, au, pool, out);
     return cudaGetLastError();
 }
@@ -1277,7 +1301,6 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 const int Gq = L.heads / L.kv_heads, nwarp = std::min(Gq, 8), groups = (Gq + nwarp - 1) / nwarp;
                 const int pad = 16 / (int)sizeof(T);
                 const size_t smem = ((size_t)nwarp * (L.dim + 32) * 4 + 15) / 16 * 16 + (size_t)32 * (L.dim + L.vdim + 2 * pad) * sizeof(T);
-                CU(cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
                 dim3 grid(A.short_rows, L.kv_heads * groups, A.n_splits);
                 attn_split_kernel<T><<<grid, nwarp * 32, smem, st>>>(A, qbuf, pool);
                 attn_merge_kernel<T><<<(A.short_rows * L.heads + 3) / 4, 128, 0, st>>>(A, mix);
@@ -1337,7 +1360,41 @@ extern "C" int smol_lm_step(SmolLm* m, const SmolLmStep* s, void* stream) {
         (s->n_want > 0 && (!s->want_rows || !s->logits)))
         return fail(SMOL_ERR_INVALID, "smol_lm_step: null array");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return m->cfg.dtype == SMOL_LM_F32 ? step_impl<float>(m, s, st) : step_impl<bf16>(m, s, st);
+    if (!m->cfg.use_graph || s->trace || s->n_tokens > kGraphMaxTokens)
+        return m->cfg.dtype == SMOL_LM_F32 ? step_impl<float>(m, s, st) : step_impl<bf16>(m, s, st);
+    // The launches of a step depend on the struct's scalars and pointers only (the arrays' contents are read on the device),
+    // except that max_pos matters through the number of key ranges alone.
+    SmolLmStep key = *s;
+    const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, m->cfg.max_context - 1) : m->cfg.max_context - 1;
+    key.max_pos = (max_pos / m->split_len + 1) * m->split_len - 1;
+    for (auto& g : m->graphs)
+        if (memcmp(&g.key, &key, sizeof(key)) == 0) {
+            CU(cudaGraphLaunch(g.exec, st));
+            m->launches += g.launches;
+            return SMOL_OK;
+        }
+    if (!m->cap_stream) CU(cudaStreamCreateWithFlags(&m->cap_stream, cudaStreamNonBlocking));
+    const int64_t before = m->launches;
+    CU(cudaStreamBeginCapture(m->cap_stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = m->cfg.dtype == SMOL_LM_F32 ? step_impl<float>(m, &key, m->cap_stream) : step_impl<bf16>(m, &key, m->cap_stream);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(m->cap_stream, &graph);
+    if (rc != SMOL_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (ce != cudaSuccess) return fail(SMOL_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(ce));
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) return fail(SMOL_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ie));
+    if (m->graphs.size() >= 64) {
+        cudaGraphExecDestroy(m->graphs.front().exec);
+        m->graphs.erase(m->graphs.begin());
+    }
+    m->graphs.push_back({key, exec, m->launches - before});
+    CU(cudaGraphLaunch(exec, st));
+    return SMOL_OK;
 }
 
 extern "C" int smol_lm_linear(SmolLm* m, const void* d_a, const void* d_w, float* d_y, int32_t M, int32_t N, int32_t K, void* stream) {

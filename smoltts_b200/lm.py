@@ -64,7 +64,7 @@ class PamasunLM:
 
     def __init__(self, config: PamasunConfig, dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None,
                  max_tokens: int = 8192, max_seqs: int = 4, page_size: int = 64, max_step_tokens: int = 2048,
-                 max_want: Optional[int] = None):
+                 max_want: Optional[int] = None, use_graph: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("smoltts_b200 needs a CUDA device: there is no CPU fallback")
         if dtype not in (torch.bfloat16, torch.float32):
@@ -77,6 +77,7 @@ class PamasunLM:
         self.max_seqs = max_seqs
         self.max_step_tokens = max_step_tokens
         self.max_want = max_want or max_step_tokens
+        self.use_graph = use_graph
         self.runs = config.layer_runs()
         self.page_pool = PagePool((max_tokens + page_size - 1) // page_size, page_size)
         self.slot_pool = SlotPool(max_seqs)
@@ -151,7 +152,7 @@ class PamasunLM:
             dtype=_capi_lm.SMOL_LM_F32 if dt == torch.float32 else _capi_lm.SMOL_LM_BF16, vocab=cfg.vocab, width=cfg.width,
             n_layers=len(cfg.layers), n_runs=len(self.runs), page_size=self.page_size, max_step_tokens=self.max_step_tokens,
             max_step_seqs=self.max_seqs, max_want=self.max_want,
-            max_context=self.page_pool.n * self.page_size, embed_scale=cfg.embedding_scale, norm_eps=cfg.norm_eps)
+            max_context=self.page_pool.n * self.page_size, use_graph=int(self.use_graph), embed_scale=cfg.embedding_scale, norm_eps=cfg.norm_eps)
         runs = (C.c_int32 * len(self.runs))(*self.runs)
         if self._h:
             self.lib.smol_lm_destroy(self._h)

@@ -42,7 +42,7 @@ def test_lm_library_exports_every_declared_symbol_and_validates_on_create():
     assert set(names) == set(_capi_lm.PROTOTYPES), (set(names) ^ set(_capi_lm.PROTOTYPES))
     lib = _capi_lm.load()
     cfg = _capi_lm.SmolLmConfig(dtype=0, vocab=64, width=32, n_layers=2, n_runs=3, page_size=16, max_step_tokens=64, max_step_seqs=2,
-                                max_want=8, max_context=256, embed_scale=1.0, norm_eps=1e-5)
+                                max_want=8, max_context=256, use_graph=1, embed_scale=1.0, norm_eps=1e-5)
     layers = (_capi_lm.SmolLmLayer * 2)()
     layers[0].mixer, layers[0].heads, layers[0].kv_heads, layers[0].dim, layers[0].vdim = 0, 4, 2, 8, 24
     layers[1].mixer, layers[1].heads, layers[1].kv_heads, layers[1].dim, layers[1].vdim, layers[1].rank = 1, 2, 2, 16, 16, 4

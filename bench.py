@@ -558,7 +558,7 @@ def measure_mimi(key: str, batch: int, frames: int, args, steps: int, warmup: in
         "realtime_factor": steps * frames * batch * world / (total_ms * 1e-3) / 12.5, "check": check,
     }
     if rank == 0 and world == 1 and batch == 1 and not args.no_cpu_baseline:
-        from oracle.mimi_oracle import MimiOracle, StreamState   # CPU leg only (the checker, never the product)
+        from oracle.mimi_oracle import MimiOracle, StreamState   # CPU leg only (the oracle, never the product)
 
         orc, st = MimiOracle(sd), StreamState()
         n = 24

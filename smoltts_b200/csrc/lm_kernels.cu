@@ -1,5 +1,5 @@
 // Hybrid language-model engine (sm_100a): ragged-batch step over a paged key/value pool and per-sequence recurrent
-// state slots.  See include/smoltts_b200_lm.h for the contract of every entry point.
+// state slots.  See include/smoltts_b200_lm.h for what every entry point takes and returns.
 //
 // Precision: the residual stream, all norms, attention scores / softmax weights and the whole recurrence run in fp32.
 // T (bf16 or float) is the element type of matrices, of the inputs of the matrix products and of the key/value pool;

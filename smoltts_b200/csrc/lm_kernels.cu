@@ -800,7 +800,9 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
     float* inv = th + A.rank;
     for (int r = threadIdx.x; r < A.rank; r += blockDim.x) th[r] = tanhf(row[5 * HD + r]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int h = warp; h < A.H; h += nw) {
+    const int c_lo = blockIdx.y * blockDim.x, c_hi = min(HD, c_lo + blockDim.x);      // this block's channels (gridDim.y slices cover HD)
+    if (c_lo >= c_hi) return;
+    for (int h = c_lo / A.d + warp; h <= (c_hi - 1) / A.d; h += nw) {
         const float* k = row + HD + h * A.d;
         float ss = 0.0f;
         for (int c = lane; c < A.d; c += 32) ss += k[c] * k[c];
@@ -808,7 +810,8 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
         if (lane == 0) inv[h] = 1.0f / sqrtf(ss + A.unit_eps);
     }
     __syncthreads();
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < HD; c += gridDim.y * blockDim.x) {
+    const int c = c_lo + threadIdx.x;
+    if (c < c_hi) {
         float lo = A.decay_bias[c];
 #pragma unroll 8
         for (int r = 0; r < A.rank; ++r) lo = fmaf(A.decay_w2[(size_t)r * HD + c], th[r], lo);
@@ -820,173 +823,203 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
     }
 }
 
-// The recurrence.  One block per (sequence, head).  Four adjacent lanes share a group of C value columns of the state:
-// lane q of the four keeps rows q*R .. q*R+R-1 (R = DK / 4, DK >= d key channels; channels beyond d are padded with
-// zero keys) of those columns in registers, and the two sums over key channels are finished with two shuffles each.
-// Per token and column j:
-//   seen = sum_i u_i S_ij;   S_ij <- w_i S_ij - (a u)_i seen + k_i v_j;   o_j = sum_i S_ij r_i.
-// Everything a token needs (r, k, u, a u, w over the key channels; v and the gate over the columns) is brought into
-// shared memory kDeltaChunk tokens at a time with cp.async, the next chunk while the current one is computed, so the
-// token loop reads no global memory; a thread's loads of the key-channel vectors serve its C columns, which keeps the
-// loop off the shared-memory bandwidth limit.  The epilogue divides each head's o by its root mean square, applies
-// the plain weight and the sigmoid gate, and writes the mixer's output in T.
+// The recurrence.  The value columns of a head's state never mix: column j follows
+//   seen = sum_i u_i S_ij;   S_ij <- w_i S_ij - (a u)_i seen + k_i v_j;   o_j = sum_i S_ij r_i
+// on its own.  So a head is cut into groups of CB columns, one block per (sequence, head, group), which puts a head on
+// several SMs.  L adjacent lanes share a column: lane q keeps the rows 4*(e*L + q) .. +3 (e = 0 .. R/4-1, R = DK / L,
+// DK >= d key channels; channels beyond d are padded with zero keys) in registers, so that the L lanes read consecutive
+// 16-byte pieces of a key-channel vector, and the two sums over key channels end with log2(L) shuffles.
+// Everything a token needs (r, k, u, a u, w over the key channels; v over the block's columns) is brought into shared
+// memory kDeltaChunk tokens at a time with cp.async, the next chunk while the current one is computed; inside a chunk
+// the next token's vectors are read into registers before the current token is computed, so the token loop waits for
+// neither global nor shared memory.  The raw o goes to global memory; delta_out_kernel finishes it.
 constexpr int kDeltaChunk = 16;
-constexpr int kDeltaArrays = 7;   // r, k, u, au, w, v, gate
 
-__host__ __device__ constexpr int delta_cols(int DK) { return DK == 16 ? 1 : 2; }
+__host__ __device__ constexpr int delta_lanes(int DK) { return DK >= 64 ? 8 : 4; }
+__host__ __device__ constexpr int delta_block_cols(int DK) { return DK * delta_lanes(DK) <= 128 ? DK : 128 / delta_lanes(DK); }
+__host__ __device__ constexpr int delta_buf_floats(int DK) { return kDeltaChunk * (5 * DK + delta_block_cols(DK)); }
 
-__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+template <int VEC> __device__ __forceinline__ void cp_async_f(float* smem, const float* gmem);
+template <> __device__ __forceinline__ void cp_async_f<1>(float* smem, const float* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem));
 }
+template <> __device__ __forceinline__ void cp_async_f<4>(float* smem, const float* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int DK>
-__device__ __forceinline__ void delta_stage(const DeltaArgs& A, float* buf, int c0, int n, int h, const float* decay, const float* ukey,
-                                            const float* aukey) {
-    const int d = A.d, HD = A.H * d;
-    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
-        const int tt = idx / d, i = idx % d;
+// Tokens c0 .. c0+n-1 of head h into one buffer: r | k | u | a u | w as [chunk][DK], then v of columns j0 .. j0+nc-1 as [chunk][CB].
+// VEC = 4 needs d, n_in and nc to be multiples of 4 (16-byte copies).
+template <int DK, int VEC>
+__device__ __forceinline__ void delta_stage(const DeltaArgs& A, float* buf, int c0, int n, int h, int j0, int nc, const float* decay,
+                                            const float* ukey, const float* aukey) {
+    constexpr int CB = delta_block_cols(DK), PL = kDeltaChunk * DK;
+    const int d = A.d, HD = A.H * d, dq = d / VEC, ncq = nc / VEC;
+    for (int idx = threadIdx.x; idx < n * dq; idx += blockDim.x) {
+        const int tt = idx / dq, i = (idx - tt * dq) * VEC;
         const float* prow = A.proj + (size_t)(c0 + tt) * A.n_in + h * d + i;
         const size_t vrow = (size_t)(c0 + tt) * HD + h * d + i;
         float* dst = buf + tt * DK + i;
-        cp_async4(dst, prow);                                       // r
-        cp_async4(dst + kDeltaChunk * DK, prow + HD);               // k
-        cp_async4(dst + 2 * kDeltaChunk * DK, ukey + vrow);
-        cp_async4(dst + 3 * kDeltaChunk * DK, aukey + vrow);
-        cp_async4(dst + 4 * kDeltaChunk * DK, decay + vrow);
-        cp_async4(dst + 5 * kDeltaChunk * DK, prow + 2 * HD);       // v
-        cp_async4(dst + 6 * kDeltaChunk * DK, prow + 3 * HD);       // gate
+        cp_async_f<VEC>(dst, prow);                         // r
+        cp_async_f<VEC>(dst + PL, prow + HD);               // k
+        cp_async_f<VEC>(dst + 2 * PL, ukey + vrow);
+        cp_async_f<VEC>(dst + 3 * PL, aukey + vrow);
+        cp_async_f<VEC>(dst + 4 * PL, decay + vrow);
+    }
+    for (int idx = threadIdx.x; idx < n * ncq; idx += blockDim.x) {
+        const int tt = idx / ncq, j = (idx - tt * ncq) * VEC;
+        cp_async_f<VEC>(buf + 5 * PL + tt * CB + j, A.proj + (size_t)(c0 + tt) * A.n_in + 2 * HD + h * d + j0 + j);
     }
 }
 
-template <int DK, class T>
-__global__ void __launch_bounds__(DK * 4 / delta_cols(DK)) delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay,
-                                                                            const float* __restrict__ ukey, const float* __restrict__ aukey,
-                                                                            float* __restrict__ state_pool, T* __restrict__ out) {
-    constexpr int C = delta_cols(DK), R = DK / 4;
-    constexpr int kBuf = kDeltaArrays * kDeltaChunk * DK;
+// One token's vectors as a lane holds them: RV 16-byte pieces of r, k, u, a u, w and the column's v.
+template <int RV>
+struct DeltaToken {
+    float4 r[RV], k[RV], u[RV], a[RV], w[RV];
+    float v;
+    __device__ __forceinline__ void load(const float4* s4, const float* s_v, int row, int row_pieces, int lanes, int plane, int cb) {
+        v = s_v[row * cb];
+#pragma unroll
+        for (int e = 0; e < RV; ++e) {
+            const float4* p = s4 + row * row_pieces + e * lanes;
+            r[e] = p[0];
+            k[e] = p[plane];
+            u[e] = p[2 * plane];
+            a[e] = p[3 * plane];
+            w[e] = p[4 * plane];
+        }
+    }
+};
+
+template <int DK>
+__global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) delta_scan_kernel(const DeltaArgs A, const float* __restrict__ decay,
+                                                                                           const float* __restrict__ ukey,
+                                                                                           const float* __restrict__ aukey,
+                                                                                           float* __restrict__ state_pool, float* __restrict__ o_raw) {
+    constexpr int L = delta_lanes(DK), CB = delta_block_cols(DK), NS = DK / CB, RV = DK / L / 4, PL = kDeltaChunk * DK;
+    constexpr int kBuf = delta_buf_floats(DK);
+    static_assert(DK % (4 * L) == 0, "every lane owns whole 16-byte pieces");
     extern __shared__ __align__(16) float sh[];
-    float* s_o = sh + 2 * kBuf;                  // [chunk][DK]
     const int d = A.d, HD = A.H * d;
-    const int seq = blockIdx.x / A.H, h = blockIdx.x % A.H;
-    const int jc = (threadIdx.x >> 2) * C, q = threadIdx.x & 3;
-    const int nw = (blockDim.x + 31) >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = blockIdx.x % NS, sh_id = blockIdx.x / NS;
+    const int seq = sh_id / A.H, h = sh_id % A.H;
+    const int j0 = group * CB;
+    if (j0 >= d) return;                          // a group of padded columns only
+    const int nc = min(CB, d - j0);
+    const int col = threadIdx.x / L, q = threadIdx.x % L, j = j0 + col;
     const int t0 = A.seq_start[seq], t1 = A.seq_start[seq + 1];
     const int slot = A.seq_slot[seq];
     if (slot < 0 || slot >= A.n_slots) {
         if (threadIdx.x == 0) atomicExch(A.err, 2);
         return;
     }
+    const bool vec = (d % 4 == 0) && (A.n_in % 4 == 0);
     for (int i = threadIdx.x; i < 2 * kBuf; i += blockDim.x) sh[i] = 0.0f;      // padded channels and columns stay zero for good
     __syncthreads();
-    delta_stage<DK>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, decay, ukey, aukey);
+    if (vec) delta_stage<DK, 4>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay, ukey, aukey);
+    else delta_stage<DK, 1>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay, ukey, aukey);
     cp_async_commit();
     float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * d;
-    float S[C][R];
+    float S[RV][4];
     const bool fresh = A.seq_pos0[seq] == 0;
 #pragma unroll
-    for (int cc = 0; cc < C; ++cc)
+    for (int e = 0; e < RV; ++e)
 #pragma unroll
-        for (int e = 0; e < R; ++e) {
-            const int i = q * R + e, j = jc + cc;
-            S[cc][e] = (!fresh && i < d && j < d && jc < DK) ? st[(size_t)i * d + j] : 0.0f;
+        for (int x = 0; x < 4; ++x) {
+            const int i = 4 * (e * L + q) + x;
+            S[e][x] = (!fresh && i < d && j < d) ? st[(size_t)i * d + j] : 0.0f;
         }
-    const bool own = jc < DK;                    // threads past the padded width only help with staging and the epilogue
+    float po = 0.0f;                              // this lane's share of the previous token's o
     int cur = 0;
     for (int c0 = t0; c0 < t1; c0 += kDeltaChunk, cur ^= 1) {
         const int n = min(kDeltaChunk, t1 - c0);
+        cp_async_wait<0>();
+        __syncthreads();                          // this chunk has landed; every thread is done with the other buffer
         if (c0 + kDeltaChunk < t1) {
-            delta_stage<DK>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, min(kDeltaChunk, t1 - c0 - kDeltaChunk), h, decay, ukey, aukey);
+            const int nn = min(kDeltaChunk, t1 - c0 - kDeltaChunk);
+            if (vec) delta_stage<DK, 4>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay, ukey, aukey);
+            else delta_stage<DK, 1>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay, ukey, aukey);
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
         const float* b = sh + cur * kBuf;
-        const float *s_r = b, *s_k = b + kDeltaChunk * DK, *s_u = b + 2 * kDeltaChunk * DK, *s_au = b + 3 * kDeltaChunk * DK,
-                    *s_w = b + 4 * kDeltaChunk * DK, *s_v = b + 5 * kDeltaChunk * DK, *s_g = b + 6 * kDeltaChunk * DK;
-        if (own) {
-            for (int tt = 0; tt < n; ++tt) {
-                const int base = tt * DK + q * R;
-                float v[C], sa[C], sb[C];
+        const float4* s4 = reinterpret_cast<const float4*>(b) + q;      // piece e of a vector of token tt: s4[(tt*DK)/4 + e*L]
+        const float* s_v = b + 5 * PL + col;
+        // two register sets take turns: while one token is computed from one set, the next token's vectors land in the other
+        DeltaToken<RV> ta, tb;
+        ta.load(s4, s_v, 0, DK / 4, L, PL / 4, CB);
+        auto step = [&](const DeltaToken<RV>& c, int tt) {
+            float sa = 0.0f, sb = 0.0f;
 #pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    v[cc] = s_v[tt * DK + jc + cc];
-                    sa[cc] = 0.0f;
-                    sb[cc] = 0.0f;
-                }
+            for (int e = 0; e < RV; ++e) {
+                sa = fmaf(c.u[e].x, S[e][0], sa);
+                sb = fmaf(c.u[e].y, S[e][1], sb);
+                sa = fmaf(c.u[e].z, S[e][2], sa);
+                sb = fmaf(c.u[e].w, S[e][3], sb);
+            }
+            float seen = sa + sb;
+            // this token's `seen` and the previous token's o go through the shuffle stages side by side
 #pragma unroll
-                for (int e = 0; e < R; e += 4) {
-                    const float4 u4 = *reinterpret_cast<const float4*>(s_u + base + e);
+            for (int s = 1; s < L; s <<= 1) {
+                const float x = __shfl_xor_sync(0xffffffffu, seen, s), y = __shfl_xor_sync(0xffffffffu, po, s);
+                seen += x;
+                po += y;
+            }
+            if (q == 0 && j < d && c0 + tt > t0) o_raw[(size_t)(c0 + tt - 1) * HD + h * d + j] = po;
+            const float ns = -seen;
+            sa = 0.0f;
+            sb = 0.0f;
 #pragma unroll
-                    for (int cc = 0; cc < C; ++cc) {
-                        sa[cc] = fmaf(u4.x, S[cc][e], sa[cc]);
-                        sb[cc] = fmaf(u4.y, S[cc][e + 1], sb[cc]);
-                        sa[cc] = fmaf(u4.z, S[cc][e + 2], sa[cc]);
-                        sb[cc] = fmaf(u4.w, S[cc][e + 3], sb[cc]);
-                    }
-                }
-                float seen[C];
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    float t = sa[cc] + sb[cc];
-                    t += __shfl_xor_sync(0xffffffffu, t, 1);
-                    t += __shfl_xor_sync(0xffffffffu, t, 2);
-                    seen[cc] = t;
-                    sa[cc] = 0.0f;
-                    sb[cc] = 0.0f;
-                }
-#pragma unroll
-                for (int e = 0; e < R; e += 4) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(s_w + base + e);
-                    const float4 a4 = *reinterpret_cast<const float4*>(s_au + base + e);
-                    const float4 k4 = *reinterpret_cast<const float4*>(s_k + base + e);
-                    const float4 r4 = *reinterpret_cast<const float4*>(s_r + base + e);
-#pragma unroll
-                    for (int cc = 0; cc < C; ++cc) {
-                        S[cc][e] = fmaf(k4.x, v[cc], fmaf(w4.x, S[cc][e], -a4.x * seen[cc]));
-                        S[cc][e + 1] = fmaf(k4.y, v[cc], fmaf(w4.y, S[cc][e + 1], -a4.y * seen[cc]));
-                        S[cc][e + 2] = fmaf(k4.z, v[cc], fmaf(w4.z, S[cc][e + 2], -a4.z * seen[cc]));
-                        S[cc][e + 3] = fmaf(k4.w, v[cc], fmaf(w4.w, S[cc][e + 3], -a4.w * seen[cc]));
-                        sa[cc] = fmaf(S[cc][e], r4.x, sa[cc]);
-                        sb[cc] = fmaf(S[cc][e + 1], r4.y, sb[cc]);
-                        sa[cc] = fmaf(S[cc][e + 2], r4.z, sa[cc]);
-                        sb[cc] = fmaf(S[cc][e + 3], r4.w, sb[cc]);
-                    }
-                }
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    float t = sa[cc] + sb[cc];
-                    t += __shfl_xor_sync(0xffffffffu, t, 1);
-                    t += __shfl_xor_sync(0xffffffffu, t, 2);
-                    if (q == 0) s_o[tt * DK + jc + cc] = t;
-                }
+            for (int e = 0; e < RV; ++e) {
+                S[e][0] = fmaf(c.a[e].x, ns, fmaf(c.w[e].x, S[e][0], c.k[e].x * c.v));
+                S[e][1] = fmaf(c.a[e].y, ns, fmaf(c.w[e].y, S[e][1], c.k[e].y * c.v));
+                S[e][2] = fmaf(c.a[e].z, ns, fmaf(c.w[e].z, S[e][2], c.k[e].z * c.v));
+                S[e][3] = fmaf(c.a[e].w, ns, fmaf(c.w[e].w, S[e][3], c.k[e].w * c.v));
+                sa = fmaf(S[e][0], c.r[e].x, sa);
+                sb = fmaf(S[e][1], c.r[e].y, sb);
+                sa = fmaf(S[e][2], c.r[e].z, sa);
+                sb = fmaf(S[e][3], c.r[e].w, sb);
+            }
+            po = sa + sb;
+        };
+        for (int tt = 0; tt < n; tt += 2) {
+            tb.load(s4, s_v, min(tt + 1, kDeltaChunk - 1), DK / 4, L, PL / 4, CB);      // a row after the last is read and dropped
+            step(ta, tt);
+            if (tt + 1 < n) {
+                ta.load(s4, s_v, min(tt + 2, kDeltaChunk - 1), DK / 4, L, PL / 4, CB);
+                step(tb, tt + 1);
             }
         }
-        __syncthreads();
-        // per-head root mean square of o, output weight and gate: one warp per token
-        for (int tt = warp; tt < n; tt += nw) {
-            float ss = 0.0f;
-            for (int c = lane; c < d; c += 32) ss = fmaf(s_o[tt * DK + c], s_o[tt * DK + c], ss);
-            ss = warp_sum(ss);
-            const float rs = 1.0f / sqrtf(ss / (float)d + A.eps);
-            for (int c = lane; c < d; c += 32)
-                out[(size_t)(c0 + tt) * HD + h * d + c] = from_f<T>(s_o[tt * DK + c] * rs * A.out_norm[h * d + c] * sigmoidf_(s_g[tt * DK + c]));
+    }
+#pragma unroll
+    for (int s = 1; s < L; s <<= 1) po += __shfl_xor_sync(0xffffffffu, po, s);
+    if (q == 0 && j < d && t1 > t0) o_raw[(size_t)(t1 - 1) * HD + h * d + j] = po;
+#pragma unroll
+    for (int e = 0; e < RV; ++e)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = 4 * (e * L + q) + x;
+            if (i < d && j < d) st[(size_t)i * d + j] = S[e][x];
         }
-        __syncthreads();          // the buffer is refilled two chunks on; s_o is rewritten next chunk
-    }
-    if (own) {
-#pragma unroll
-        for (int cc = 0; cc < C; ++cc)
-#pragma unroll
-            for (int e = 0; e < R; ++e) {
-                const int i = q * R + e, j = jc + cc;
-                if (i < d && j < d) st[(size_t)i * d + j] = S[cc][e];
-            }
-    }
+}
+
+// End of the recurrent mixer: each head's o divided by its root mean square, times the plain weight, times the sigmoid
+// gate, written in T.  One warp per (token, head).
+template <class T>
+__global__ void delta_out_kernel(const DeltaArgs A, const float* __restrict__ o_raw, T* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= A.n_tokens * A.H) return;
+    const int t = unit / A.H, h = unit % A.H, d = A.d, HD = A.H * d;
+    const float* o = o_raw + (size_t)t * HD + h * d;
+    const float* gate = A.proj + (size_t)t * A.n_in + 3 * HD + h * d;
+    float ss = 0.0f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(o[c], o[c], ss);
+    ss = warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)d + A.eps);
+    for (int c = lane; c < d; c += 32) out[(size_t)t * HD + h * d + c] = from_f<T>(o[c] * rs * A.out_norm[h * d + c] * sigmoidf_(gate[c]));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1041,7 +1074,7 @@ struct SmolLm {
     size_t page_elems = 0, slot_floats = 0, esize = 2;
     int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
     // workspace carving (byte offsets)
-    size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_q, o_hw, o_err, o_part, total;
+    size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_oraw, o_q, o_hw, o_err, o_part, total;
     int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
     char* ws = nullptr;
     void* pages = nullptr;
@@ -1127,6 +1160,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     m->o_dec = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
     m->o_u = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
     m->o_au = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
+    m->o_oraw = carve(T * (size_t)std::max(m->max_hd, 1) * 4);
     m->o_q = carve(T * (size_t)std::max(m->max_q, 1) * E);
     m->o_hw = carve((size_t)cfg->max_want * D * E);
     m->o_err = carve(256);
@@ -1147,17 +1181,16 @@ extern "C" size_t smol_lm_workspace_bytes(const SmolLm* m) { return m ? m->total
 extern "C" int64_t smol_lm_launch_count(const SmolLm* m) { return m ? m->launches : 0; }
 extern "C" int32_t* smol_lm_error_word(SmolLm* m) { return (m && m->bound) ? reinterpret_cast<int32_t*>(m->ws + m->o_err) : nullptr; }
 
-template <int DK, class T>
+template <int DK>
 static cudaError_t scan_attribute() {
-    return cudaFuncSetAttribute(delta_scan_kernel<DK, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)((2 * kDeltaArrays * kDeltaChunk * DK + kDeltaChunk * DK) * sizeof(float)));
+    return cudaFuncSetAttribute(delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * delta_buf_floats(DK) * sizeof(float)));
 }
 template <class T>
 static cudaError_t set_kernel_attributes() {
-    cudaError_t e = scan_attribute<16, T>();
-    if (e == cudaSuccess) e = scan_attribute<32, T>();
-    if (e == cudaSuccess) e = scan_attribute<64, T>();
-    if (e == cudaSuccess) e = scan_attribute<128, T>();
+    cudaError_t e = scan_attribute<16>();
+    if (e == cudaSuccess) e = scan_attribute<32>();
+    if (e == cudaSuccess) e = scan_attribute<64>();
+    if (e == cudaSuccess) e = scan_attribute<128>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     return e;
 }
@@ -1221,12 +1254,11 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
     return cudaGetLastError();
 }
 
-template <int DK, class T>
-static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec, const float* u, const float* au, float* pool, T* out,
+template <int DK>
+static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec, const float* u, const float* au, float* pool, float* o_raw,
                                cudaStream_t st) {
-    const int threads = std::max(32, DK * 4 / delta_cols(DK));
-    const size_t smem = (size_t)(2 * kDeltaArrays * kDeltaChunk * DK + kDeltaChunk * DK) * sizeof(float);
-    delta_scan_kernel<DK, T><<<n_seqs * A.H, threads, smem, st>>>(A, dec, u, au, pool, out);
+    constexpr int threads = delta_block_cols(DK) * delta_lanes(DK), groups = DK / delta_block_cols(DK);
+    delta_scan_kernel<DK><<<n_seqs * A.H * groups, threads, 2 * delta_buf_floats(DK) * sizeof(float), st>>>(A, dec, u, au, pool, o_raw);
     return cudaGetLastError();
 }
 
@@ -1244,6 +1276,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     float* dec = reinterpret_cast<float*>(m->ws + m->o_dec);
     float* uk = reinterpret_cast<float*>(m->ws + m->o_u);
     float* auk = reinterpret_cast<float*>(m->ws + m->o_au);
+    float* oraw = reinterpret_cast<float*>(m->ws + m->o_oraw);
     T* qbuf = reinterpret_cast<T*>(m->ws + m->o_q);
     T* hw = reinterpret_cast<T*>(m->ws + m->o_hw);
     int32_t* err = reinterpret_cast<int32_t*>(m->ws + m->o_err);
@@ -1317,12 +1350,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.slot_floats = m->slot_floats; A.state_off = R.state_off; A.n_slots = m->n_slots; A.err = err;
             delta_prep_kernel<<<dim3(Tn, (L.heads * L.dim + 127) / 128), 128, (L.rank + L.heads) * sizeof(float), st>>>(A, dec, uk, auk);
             cudaError_t e;
-            if (L.dim <= 16) e = launch_scan<16, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
-            else if (L.dim <= 32) e = launch_scan<32, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
-            else if (L.dim <= 64) e = launch_scan<64, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
-            else e = launch_scan<128, T>(A, s->n_seqs, dec, uk, auk, m->slots, mix, st);
+            if (L.dim <= 16) e = launch_scan<16>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
+            else if (L.dim <= 32) e = launch_scan<32>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
+            else if (L.dim <= 64) e = launch_scan<64>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
+            else e = launch_scan<128>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
             CU(e);
-            m->launches += 2;
+            delta_out_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(A, oraw, mix);
+            m->launches += 3;
             mix_cols = L.heads * L.dim;
         }
         CU(linear<T>(m, mix, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));

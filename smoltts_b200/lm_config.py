@@ -34,7 +34,8 @@ class MixerSpec:
         if kind not in MIXER_KINDS:
             raise ValueError(f"unknown mixer type {kind!r}; have {sorted(MIXER_KINDS)}")
         if kind == "attention":
-            return cls(kind, int(d["heads"]), int(d["dim"]), int(d["kv_heads"]), int(d["vdim"]), float(d["scale"]))
+            # kv_heads and vdim default to heads and dim (plain multi-head attention with square heads)
+            return cls(kind, int(d["heads"]), int(d["dim"]), int(d.get("kv_heads", d["heads"])), int(d.get("vdim", d["dim"])), float(d["scale"]))
         return cls(kind, int(d["heads"]), int(d["dim"]), int(d["heads"]), int(d["dim"]))
 
     def to_dict(self) -> Dict[str, Any]:

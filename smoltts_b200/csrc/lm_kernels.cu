@@ -17,6 +17,8 @@
 #include "../../include/smoltts_b200_lm.h"
 #include "common.cuh"
 #include "sampler.cuh"
+#include "tmap_host.h"
+#include "umma.cuh"
 
 #define SMOL_OK 0
 #define SMOL_ERR_INVALID (-1)
@@ -324,6 +326,49 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(const bf16* __restrict__
         const float t = warp_sum(acc[m]);
         if (lane == 0 && m < M) y[(size_t)m * N + n] = t;
     }
+}
+
+// Matrix product for many rows (prompt portions), bf16 on the 5th-generation tensor cores: the library's tcgen05 tile
+// (umma.cuh: TMA loads into a 128-byte-swizzled ring, accumulators in tensor memory) over 128 rows x kTcTileN columns,
+// one persistent CTA per SM walking the tiles; row tiles that share a weight tile run on neighbouring CTAs.  Rows and
+// columns outside the matrices are zero-filled by TMA (a partial last K stage adds zeros); rows past M of the activation
+// buffer hold stale values whose accumulator lanes are never stored.
+constexpr int kTcTileN = umma::kMaxN;
+constexpr int kTcThreads = 512;
+constexpr int kTcSmemBytes = umma::kRingBytes + 1024;
+constexpr int kTcMinRows = 257;          // below this the mma.sync tiles fill the GPU better than 128-row tiles
+
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                                                                float* __restrict__ y, int M, int N, int K) {
+    extern __shared__ unsigned char tc_smem[];
+    __shared__ umma::Bars bars;
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem) + 1023) & ~(uintptr_t)1023);
+    umma::Pipe pipe;
+    umma::setup(&bars, pipe, (uint32_t)umma::kAcc, 2u);
+    const int m_tiles = (M + umma::kM - 1) / umma::kM, n_tiles = (N + kTcTileN - 1) / kTcTileN;
+    const int k_pad = (K + umma::kBK - 1) / umma::kBK * umma::kBK;
+    const bool vec = N % 4 == 0;
+    for (int u = blockIdx.x; u < m_tiles * n_tiles; u += gridDim.x) {
+        const int m0 = (u % m_tiles) * umma::kM, n0 = (u / m_tiles) * kTcTileN;
+        umma::BSrc b0, b1;
+        b0.tm = &tm_w; b0.row0 = n0; b0.n = kTcTileN; b0.box = kTcTileN;
+        b1.tm = nullptr; b1.row0 = 0; b1.n = 0; b1.box = kTcTileN;
+        umma::tile_mma_tma<kTcThreads>(ring, &bars, pipe, k_pad, &tm_a, m0, b0, b1);
+        umma::tile_epilogue(&bars, kTcTileN, [&](int row, int c0, const float (&acc)[8]) {
+            const int m = m0 + row, n = n0 + c0;
+            if (m >= M || n >= N) return;
+            float* out = y + (size_t)m * N + n;
+            if (vec && n + 8 <= N) {
+                *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(out + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (n + e < N) out[e] = acc[e];
+            }
+        }, kTcTileN);
+    }
+    umma::teardown(&bars);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1081,6 +1126,8 @@ struct SmolLm {
     float* slots = nullptr;
     int n_pages = 0, n_slots = 0;
     bool bound = false;
+    bool tc_ready = false;      // the tcgen05 matrix product may be launched (attribute set, driver entry point found)
+    int n_sms = 1;
     int64_t launches = 0;
     // small steps (decoding) are captured once per shape into a CUDA graph and replayed
     struct Captured { SmolLmStep key; cudaGraphExec_t exec; int64_t launches; };
@@ -1205,6 +1252,11 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
     if (!g->embed || !g->head || !g->final_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: missing global weights");
     CU(set_kernel_attributes<float>());
     CU(set_kernel_attributes<bf16>());
+    int dev = 0;
+    CU(cudaGetDevice(&dev));
+    CU(cudaDeviceGetAttribute(&m->n_sms, cudaDevAttrMultiProcessorCount, dev));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
+    m->tc_ready = smol::tensor_map_encoder() != nullptr && m->n_sms > 0;
     m->g = *g;
     m->ws = static_cast<char*>(d_workspace);
     m->pages = d_pages;
@@ -1234,6 +1286,17 @@ cudaError_t linear<float>(SmolLm* m, const float* a, const float* w, float* y, i
 
 template <>
 cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int M, int N, int K, cudaStream_t st) {
+    const bool aligned = K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0;
+    if (M >= kTcMinRows && N >= kTcTileN && K >= smol::umma::kBK && aligned && m->tc_ready && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+        CUtensorMap ta, tw;
+        if (smol::make_tensor_map_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)smol::umma::kM) &&
+            smol::make_tensor_map_2d(&tw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)kTcTileN)) {
+            const int tiles = ((M + smol::umma::kM - 1) / smol::umma::kM) * ((N + kTcTileN - 1) / kTcTileN);
+            gemm_tc_kernel<<<std::min(tiles, m->n_sms), kTcThreads, kTcSmemBytes, st>>>(ta, tw, y, M, N, K);
+            m->launches++;
+            return cudaGetLastError();
+        }
+    }
     if (M <= 8 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
         const int grid = (N + 7) / 8;
         if (M == 1) gemv_bf16_kernel<1><<<grid, 256, 0, st>>>(a, w, y, M, N, K);

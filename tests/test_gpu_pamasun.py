@@ -218,7 +218,8 @@ def test_linear_kernels_against_torch():
     model, _, _ = engine_and_oracle(config([attn(ff=0)]), seed=9)
     modelb, _, _ = engine_and_oracle(config([attn(ff=0)]), seed=9, dtype=BF16)
     g = torch.Generator(device="cuda").manual_seed(0)
-    for M, N, K in ((1, 200, 72), (5, 33, 40), (17, 64, 256), (70, 130, 100), (300, 96, 35), (129, 257, 64)):
+    for M, N, K in ((1, 200, 72), (5, 33, 40), (17, 64, 256), (70, 130, 100), (300, 96, 35), (129, 257, 64),
+                    (260, 333, 72), (515, 96, 64), (1024, 768, 256), (300, 100, 136), (257, 97, 1000)):      # 257 rows and more: tcgen05 tiles
         a = torch.randn(M, K, device="cuda", generator=g)
         w = torch.randn(N, K, device="cuda", generator=g)
         ref = a.double() @ w.double().T
@@ -226,6 +227,31 @@ def test_linear_kernels_against_torch():
         ab, wb = a.bfloat16(), w.bfloat16()
         refb = ab.double() @ wb.double().T
         assert float((modelb.linear(ab, wb).double() - refb).abs().max()) < 1e-4 * K ** 0.5
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_long_portions_take_the_large_tile_path(dtype):
+    """Steps of several hundred tokens (the matrix products change kernels with the row count) against the oracle, against
+    short portions of the same prompt, and beside a decoding request in the same step."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([delta(heads=2, dim=32, ff=160, rank=8), attn(heads=4, kv_heads=2, dim=32, vdim=24, scale=0.2, ff=104)], vocab=131, width=128)
+    model, orc, _ = engine_and_oracle(cfg, seed=11, dtype=dtype, edit=peaky, page_size=64, max_tokens=1024, max_step_tokens=512)
+    toks, other = tokens(700, 131, 30), tokens(40, 131, 31)
+    want, want_o = orc.forward(toks), orc.forward(other)
+    b = TokenBatcher(model)
+    b.feed([("o", other[:30], [])])
+    got = [b.feed([("a", toks[:300], list(range(300)))])]
+    out = b.feed([("a", toks[300:690], list(range(390))), ("o", other[30:31], [0])])
+    got.append(out[:390])
+    assert rel_err(out[390:], want_o[30:31]) < TOL[dtype]
+    got.append(b.feed([("a", toks[690:], list(range(10)))], end=["a", "o"]))
+    long = torch.cat(got)
+    assert rel_err(long, want) < TOL[dtype]
+    short = torch.cat([b.feed([("s", toks[lo:lo + 100], list(range(100)))], end=["s"] if lo == 600 else []) for lo in range(0, 700, 100)])
+    assert rel_err(short, want) < TOL[dtype]
+    assert rel_err(long, short) < (1e-4 if dtype == F32 else TOL[dtype])
+    model.check_device_errors()
 
 
 def test_capacity_errors_are_raised_not_faulted():

@@ -697,6 +697,8 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
     }
 }
 
+// The exponentials and the penalty's logarithm use the hardware approximations (relative error about 2^-22): this form
+// serves bf16 only, whose products carry 2^-9.
 template <int DP>
 __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const bf16* __restrict__ qbuf, const bf16* __restrict__ pool,
                                                          bf16* __restrict__ out) {
@@ -705,7 +707,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     __shared__ __align__(16) bf16 Vs[64 * LD];
     const int s = blockIdx.y;
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
-    const int tile = blockIdx.x;
+    const int tile = gridDim.x - 1 - blockIdx.x;      // the tiles with the most keys start first
     if (n <= kShortSeq || tile * 64 >= n) return;
     const int h = blockIdx.z, g = h / (A.H / A.G);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -766,7 +768,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
                 for (int e = 0; e < 4; ++e) {
                     const int j = j0 + nt * 8 + tq * 2 + (e & 1);
                     const int i = e < 2 ? i_a : i_b;
-                    const float v = j <= i ? S[nt][e] * A.scale - r1 * log1pf(r2 * (float)(i - j)) : -INFINITY;
+                    const float v = j <= i ? S[nt][e] * A.scale - r1 * __logf(1.0f + r2 * (float)(i - j)) : -INFINITY;
                     S[nt][e] = v;
                     if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                 }
@@ -775,7 +777,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
             const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-            const float ca = expf(m_a - mn_a), cb = expf(m_b - mn_b);
+            const float ca = __expf(m_a - mn_a), cb = __expf(m_b - mn_b);
             m_a = mn_a; m_b = mn_b;
             l_a *= ca; l_b *= cb;
 #pragma unroll
@@ -785,7 +787,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             for (int nt = 0; nt < 8; ++nt) {
                 float p[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) p[e] = expf(S[nt][e] - (e < 2 ? mn_a : mn_b));
+                for (int e = 0; e < 4; ++e) p[e] = __expf(S[nt][e] - (e < 2 ? mn_a : mn_b));
                 l_a += p[0] + p[1];
                 l_b += p[2] + p[3];
                 float ph[4];

@@ -674,7 +674,16 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
 }
 
 // rows x cols bf16 from `src(row)` (nullptr: a row of zeros) into dst[row * LD + col], columns cols .. DP-1 zeroed.
-template <int DP, class RowPtr>
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 64 rows of `cols` bf16 into a [64][DP + 8] tile; src(row) is the row's address or nullptr (zero row).  ASYNC: whole
+// 16-byte pieces of aligned rows go by cp.async (the caller commits and waits); everything else is stored directly.
+template <int DP, bool ASYNC, class RowPtr>
 __device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
     constexpr int LD = DP + 8;
     const bool vec = (cols % 8) == 0;
@@ -684,6 +693,10 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (p && c < cols) {
             if (vec && (reinterpret_cast<uintptr_t>(p) % 16) == 0) {
+                if (ASYNC) {
+                    cp_async16(dst + row * LD + c, p + c);
+                    continue;
+                }
                 v = *reinterpret_cast<const uint4*>(p + c);
             } else {
                 uint16_t hh[8];
@@ -702,9 +715,10 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
 template <int DP>
 __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const bf16* __restrict__ qbuf, const bf16* __restrict__ pool,
                                                          bf16* __restrict__ out) {
-    constexpr int LD = DP + 8;
-    __shared__ __align__(16) bf16 Ks[64 * LD];
-    __shared__ __align__(16) bf16 Vs[64 * LD];
+    constexpr int LD = DP + 8, kTile = 64 * LD;
+    extern __shared__ __align__(16) unsigned char flash_smem[];      // keys [2][64][LD], values [2][64][LD]: two tiles in turn
+    bf16* Ks = reinterpret_cast<bf16*>(flash_smem);
+    bf16* Vs = Ks + 2 * kTile;
     const int s = blockIdx.y;
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
     const int tile = gridDim.x - 1 - blockIdx.x;      // the tiles with the most keys start first
@@ -714,7 +728,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     const int pos0 = A.tok_pos[t0];
     const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
     // queries of the tile -> A fragments
-    stage_rows<DP>(Ks, A.d, [&](int row) -> const bf16* {
+    stage_rows<DP, false>(Ks, A.d, [&](int row) -> const bf16* {
         return tile * 64 + row < n ? qbuf + ((size_t)(t0 + tile * 64 + row) * A.H + h) * A.d : nullptr;
     });
     __syncthreads();
@@ -738,15 +752,29 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     for (int nt = 0; nt < DP / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[nt][e] = 0.0f;
-    for (int j0 = 0; j0 <= last_pos; j0 += 64) {
+    // the next tile of keys and values is on its way (cp.async) while the current one is multiplied
+    auto stage_tile = [&](int j0, int buf) {
         auto row_of = [&](int row, size_t off, int width) -> const bf16* {
             const int j = j0 + row;
             if (j > last_pos) return nullptr;
             return pool + (size_t)bt[j / A.page_size] * A.page_elems + off + ((size_t)g * A.page_size + j % A.page_size) * width;
         };
-        stage_rows<DP>(Ks, A.d, [&](int row) { return row_of(row, A.k_off, A.d); });
-        stage_rows<DP>(Vs, A.dv, [&](int row) { return row_of(row, A.v_off, A.dv); });
+        stage_rows<DP, true>(Ks + buf * kTile, A.d, [&](int row) { return row_of(row, A.k_off, A.d); });
+        stage_rows<DP, true>(Vs + buf * kTile, A.dv, [&](int row) { return row_of(row, A.v_off, A.dv); });
+        cp_async_commit_group();
+    };
+    stage_tile(0, 0);
+    int buf = 0;
+    for (int j0 = 0; j0 <= last_pos; j0 += 64, buf ^= 1) {
+        if (j0 + 64 <= last_pos) {
+            stage_tile(j0 + 64, buf ^ 1);
+            cp_async_wait_group<1>();
+        } else {
+            cp_async_wait_group<0>();
+        }
         __syncthreads();
+        const bf16* Kt = Ks + buf * kTile;
+        const bf16* Vt = Vs + buf * kTile;
         if (j0 <= pos0 + tile * 64 + warp * 16 + 15) {          // this warp's rows see at least one key of the tile
             float S[8][4];
 #pragma unroll
@@ -757,7 +785,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             for (int kk = 0; kk < DP / 16; ++kk)
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
-                    const bf16* p = Ks + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
+                    const bf16* p = Kt + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
                     mma_bf16_16816(S[nt], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], *reinterpret_cast<const uint32_t*>(p),
                                    *reinterpret_cast<const uint32_t*>(p + 8));
                 }
@@ -801,7 +829,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
 #pragma unroll
                 for (int nt = 0; nt < DP / 8; ++nt) {
                     uint32_t b0, b1;
-                    ldmatrix_x2_trans(b0, b1, Vs + (k2 * 16 + (lane & 15)) * LD + nt * 8);
+                    ldmatrix_x2_trans(b0, b1, Vt + (k2 * 16 + (lane & 15)) * LD + nt * 8);
                     mma_bf16_16816(o[nt], hi[2 * k2][0], hi[2 * k2][1], hi[2 * k2 + 1][0], hi[2 * k2 + 1][1], b0, b1);
                     mma_bf16_16816(o[nt], lo[2 * k2][0], lo[2 * k2][1], lo[2 * k2 + 1][0], lo[2 * k2 + 1][1], b0, b1);
                 }
@@ -1234,6 +1262,8 @@ template <int DK>
 static cudaError_t scan_attribute() {
     return cudaFuncSetAttribute(delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * delta_buf_floats(DK) * sizeof(float)));
 }
+static constexpr int flash_smem_bytes(int DP) { return 4 * 64 * (DP + 8) * (int)sizeof(bf16); }
+
 template <class T>
 static cudaError_t set_kernel_attributes() {
     cudaError_t e = scan_attribute<16>();
@@ -1241,6 +1271,7 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = scan_attribute<64>();
     if (e == cudaSuccess) e = scan_attribute<128>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128));
     return e;
 }
 
@@ -1385,9 +1416,9 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                     const bf16* qb = reinterpret_cast<const bf16*>(qbuf);
                     const bf16* pl = reinterpret_cast<const bf16*>(pool);
                     bf16* mx = reinterpret_cast<bf16*>(mix);
-                    if (hp <= 32) attn_flash_kernel<32><<<grid, 128, 0, st>>>(A, qb, pl, mx);
-                    else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, 0, st>>>(A, qb, pl, mx);
-                    else attn_flash_kernel<128><<<grid, 128, 0, st>>>(A, qb, pl, mx);
+                    if (hp <= 32) attn_flash_kernel<32><<<grid, 128, flash_smem_bytes(32), st>>>(A, qb, pl, mx);
+                    else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, flash_smem_bytes(64), st>>>(A, qb, pl, mx);
+                    else attn_flash_kernel<128><<<grid, 128, flash_smem_bytes(128), st>>>(A, qb, pl, mx);
                 } else {
                     // every row, also those of short sequences
                     const int au = Tn * L.heads;

@@ -910,7 +910,7 @@ __global__ void delta_prep_kernel(const DeltaArgs A, float* __restrict__ decay, 
 // neither global nor shared memory.  The raw o goes to global memory; delta_out_kernel finishes it.
 constexpr int kDeltaChunk = 16;
 
-__host__ __device__ constexpr int delta_lanes(int DK) { return DK >= 64 ? 8 : 4; }
+__host__ __device__ constexpr int delta_lanes(int DK) { return DK >= 256 ? 16 : DK >= 64 ? 8 : 4; }
 __host__ __device__ constexpr int delta_block_cols(int DK) { return DK * delta_lanes(DK) <= 128 ? DK : 128 / delta_lanes(DK); }
 __host__ __device__ constexpr int delta_buf_floats(int DK) { return kDeltaChunk * (5 * DK + delta_block_cols(DK)); }
 
@@ -1207,7 +1207,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_vdim = std::max(m->max_vdim, L.vdim);
             m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
         } else if (L.mixer == SMOL_LM_MIX_GENERAL_DELTA) {
-            if (L.dim > 128) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 128"); }
+            if (L.dim > 256) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256"); }
             if (L.rank < 1) { delete m; return fail(SMOL_ERR_INVALID, "recurrent mixer: rank must be positive"); }
             r.state_off = m->slot_floats;
             m->slot_floats += (size_t)L.heads * L.dim * L.dim;
@@ -1270,6 +1270,7 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = scan_attribute<32>();
     if (e == cudaSuccess) e = scan_attribute<64>();
     if (e == cudaSuccess) e = scan_attribute<128>();
+    if (e == cudaSuccess) e = scan_attribute<256>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128));
     return e;
@@ -1449,7 +1450,8 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             if (L.dim <= 16) e = launch_scan<16>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
             else if (L.dim <= 32) e = launch_scan<32>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
             else if (L.dim <= 64) e = launch_scan<64>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
-            else e = launch_scan<128>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
+            else if (L.dim <= 128) e = launch_scan<128>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
+            else e = launch_scan<256>(A, s->n_seqs, dec, uk, auk, m->slots, oraw, st);
             CU(e);
             delta_out_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(A, oraw, mix);
             m->launches += 3;

@@ -40,8 +40,10 @@ def peaky(w):
     [attn(ff=0)], [delta(ff=0)], [attn(heads=1, kv_heads=1, dim=8, vdim=8, ff=40)], [delta(heads=1, dim=32, ff=0, rank=3)],
     [attn(heads=6, kv_heads=2, dim=24, vdim=40, scale=0.2, ff=0)], [delta(heads=2, dim=48, ff=0, rank=16)],
     [delta(heads=1, dim=128, ff=0)], [attn(heads=3, kv_heads=1, dim=12, vdim=20, scale=0.3, ff=0)],
-    [attn(heads=2, kv_heads=1, dim=128, vdim=64, scale=0.09, ff=0)], [attn(heads=2, kv_heads=2, dim=40, vdim=136, scale=0.15, ff=0)]],
-    ids=["attention", "delta", "mha+mlp", "delta32", "gqa-odd", "delta48", "delta128", "attn-unaligned", "attn128", "attn-wide-v"])
+    [attn(heads=2, kv_heads=1, dim=128, vdim=64, scale=0.09, ff=0)], [attn(heads=2, kv_heads=2, dim=40, vdim=136, scale=0.15, ff=0)],
+    [delta(heads=1, dim=160, ff=0, rank=4)], [delta(heads=2, dim=256, ff=0, rank=12)], [delta(heads=2, dim=20, ff=0, rank=7)]],
+    ids=["attention", "delta", "mha+mlp", "delta32", "gqa-odd", "delta48", "delta128", "attn-unaligned", "attn128", "attn-wide-v",
+         "delta160", "delta256", "delta20-odd-rank"])
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
 def test_each_mechanism_alone(layers, dtype):
     cfg = config(layers, vocab=61, width=72)

@@ -1241,10 +1241,11 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     m->o_q = carve(T * (size_t)std::max(m->max_q, 1) * E);
     m->o_hw = carve((size_t)cfg->max_want * D * E);
     m->o_err = carve(256);
-    // few-token attention: key ranges of split_len positions, at most 64 of them per row
+    // few-token attention: key ranges of split_len positions (64 while the context stays below 16 384: a decoding row
+    // then spreads over context / 64 blocks per key/value head), at most 256 of them per row; ranges are launched four at a time
     const int ctx = std::max(cfg->max_context, 1);
-    m->split_len = std::max(256, ((ctx + 63) / 64 + 63) / 64 * 64);
-    m->max_splits = (ctx + m->split_len - 1) / m->split_len;
+    m->split_len = std::max(64, ((ctx + 255) / 256 + 63) / 64 * 64);
+    m->max_splits = ((ctx + m->split_len - 1) / m->split_len + 3) / 4 * 4;
     m->o_part = carve((size_t)cfg->max_step_seqs * kShortSeq * m->max_heads * m->max_splits * (m->max_vdim + 2) * 4);
     m->total = o;
     *out = m;
@@ -1408,7 +1409,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             const int min_n = s->min_seq_tokens > 0 ? s->min_seq_tokens : 1;
             const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
             const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
-            A.n_splits = max_pos / m->split_len + 1;
+            A.n_splits = std::min(m->max_splits, (max_pos / m->split_len + 4) / 4 * 4);
             const int hp = std::max(L.dim, L.vdim);
             const bool flash = sizeof(T) == 2 && hp <= 128;
             if (max_n > kShortSeq) {
@@ -1498,7 +1499,7 @@ extern "C" int smol_lm_step(SmolLm* m, const SmolLmStep* s, void* stream) {
     // except that max_pos matters through the number of key ranges alone.
     SmolLmStep key = *s;
     const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, m->cfg.max_context - 1) : m->cfg.max_context - 1;
-    key.max_pos = (max_pos / m->split_len + 1) * m->split_len - 1;
+    key.max_pos = std::min(m->cfg.max_context - 1, (max_pos / m->split_len + 4) / 4 * 4 * m->split_len - 1);
     for (auto& g : m->graphs)
         if (memcmp(&g.key, &key, sizeof(key)) == 0) {
             CU(cudaGraphLaunch(g.exec, st));

@@ -116,26 +116,67 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
     for (int c = threadIdx.x; c < D; c += blockDim.x) hn[o + c] = from_f<T>(row[c] * r2 * (1.0f + wn[c]));
 }
 
-// PolyNorm: out = a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e over a token's feed-forward vector.
+// Three sums over the block at once; every thread gets the results.  `red` holds 3 x 33 floats.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (*red)[33]) {
+    a = warp_sum(a);
+    b = warp_sum(b);
+    c = warp_sum(c);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) { red[0][w] = a; red[1][w] = b; red[2][w] = c; }
+    __syncthreads();
+    if (w < 3) {
+        float t = l < nw ? red[w][l] : 0.0f;
+        t = warp_sum(t);
+        if (l == 0) red[w][32] = t;
+    }
+    __syncthreads();
+    a = red[0][32];
+    b = red[1][32];
+    c = red[2][32];
+}
+
+template <class T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// PolyNorm: out = a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e over a token's feed-forward vector.  The three sums
+// are taken in one pass and reduced together; rows whose length is a multiple of 4 move as 16-byte pieces.
 template <class T>
 __global__ void polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coef, float eps, int F, T* __restrict__ out) {
-    __shared__ float red[33];
+    __shared__ float red[3][33];
     const size_t o = (size_t)blockIdx.x * F;
+    const bool vec = F % 4 == 0;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
-    for (int c = threadIdx.x; c < F; c += blockDim.x) {
-        const float v = z[o + c], v2 = v * v;
+    auto add = [&](float v) {
+        const float v2 = v * v;
         s2 += v2;
         s4 += v2 * v2;
         s6 += v2 * v2 * v2;
+    };
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(z + o + c);
+            add(v.x); add(v.y); add(v.z); add(v.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < F; c += blockDim.x) add(z[o + c]);
     }
-    s2 = block_sum(s2, red);
-    s4 = block_sum(s4, red);
-    s6 = block_sum(s6, red);
+    block_sum3(s2, s4, s6, red);
     const float a = coef[0] / sqrtf(s2 / (float)F + eps), b = coef[1] / sqrtf(s4 / (float)F + eps),
                 cc = coef[2] / sqrtf(s6 / (float)F + eps), e = coef[3];
-    for (int c = threadIdx.x; c < F; c += blockDim.x) {
-        const float v = z[o + c];
-        out[o + c] = from_f<T>(a * v + b * v * v + cc * v * v * v + e);
+    auto f = [&](float v) { return a * v + b * v * v + cc * v * v * v + e; };
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(z + o + c);
+            store4<T>(out + o + c, f(v.x), f(v.y), f(v.z), f(v.w));
+        }
+    } else {
+        for (int c = threadIdx.x; c < F; c += blockDim.x) out[o + c] = from_f<T>(f(z[o + c]));
     }
 }
 
@@ -295,36 +336,55 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
         }
 }
 
-// Matrix product for very few rows (decoding): one warp per output column, lanes cut K into 16-byte pieces; the weights are
-// streamed once, the MR activation rows come from L1/L2.  Needs K % 8 == 0 and 16-byte aligned operands.
-template <int MR>
+// Matrix product for very few rows (decoding): WPC warps per output column (each a 1/WPC interleaved share of K, the
+// shares added in a fixed order), lanes cut K into 16-byte pieces; the weights are streamed once, the MR activation
+// rows come from L1/L2.  WPC follows from N alone (narrow products get more warps per column so that the grid still
+// covers the SMs).  Needs K % 8 == 0 and 16-byte aligned operands.
+template <int MR, int WPC>
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ y,
                                                         int M, int N, int K) {
-    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (n >= N) return;
+    __shared__ float part[8][MR];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, kw = warp % WPC;
+    const int n = blockIdx.x * (8 / WPC) + warp / WPC;
+    const bool valid = n < N;
     float acc[MR];
 #pragma unroll
     for (int m = 0; m < MR; ++m) acc[m] = 0.0f;
-    const bf16* wr = w + (size_t)n * K;
-    for (int k = lane * 8; k < K; k += 256) {
-        const uint4 wv = ldg_stream(wr + k);
-        const float w0 = bf_lo(wv.x), w1 = bf_hi(wv.x), w2 = bf_lo(wv.y), w3 = bf_hi(wv.y), w4 = bf_lo(wv.z), w5 = bf_hi(wv.z),
-                    w6 = bf_lo(wv.w), w7 = bf_hi(wv.w);
+    if (valid) {
+        const bf16* wr = w + (size_t)n * K;
+        for (int k = (kw * 32 + lane) * 8; k < K; k += 256 * WPC) {
+            const uint4 wv = ldg_stream(wr + k);
+            const float w0 = bf_lo(wv.x), w1 = bf_hi(wv.x), w2 = bf_lo(wv.y), w3 = bf_hi(wv.y), w4 = bf_lo(wv.z), w5 = bf_hi(wv.z),
+                        w6 = bf_lo(wv.w), w7 = bf_hi(wv.w);
 #pragma unroll
-        for (int m = 0; m < MR; ++m) {
-            if (m < M) {
-                const uint4 av = ldg_v4(a + (size_t)m * K + k);
-                float t = acc[m];
-                t = fmaf(bf_lo(av.x), w0, t); t = fmaf(bf_hi(av.x), w1, t); t = fmaf(bf_lo(av.y), w2, t); t = fmaf(bf_hi(av.y), w3, t);
-                t = fmaf(bf_lo(av.z), w4, t); t = fmaf(bf_hi(av.z), w5, t); t = fmaf(bf_lo(av.w), w6, t); t = fmaf(bf_hi(av.w), w7, t);
-                acc[m] = t;
+            for (int m = 0; m < MR; ++m) {
+                if (m < M) {
+                    const uint4 av = ldg_v4(a + (size_t)m * K + k);
+                    float t = acc[m];
+                    t = fmaf(bf_lo(av.x), w0, t); t = fmaf(bf_hi(av.x), w1, t); t = fmaf(bf_lo(av.y), w2, t); t = fmaf(bf_hi(av.y), w3, t);
+                    t = fmaf(bf_lo(av.z), w4, t); t = fmaf(bf_hi(av.z), w5, t); t = fmaf(bf_lo(av.w), w6, t); t = fmaf(bf_hi(av.w), w7, t);
+                    acc[m] = t;
+                }
             }
         }
     }
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
         const float t = warp_sum(acc[m]);
-        if (lane == 0 && m < M) y[(size_t)m * N + n] = t;
+        if (WPC == 1) {
+            if (lane == 0 && valid && m < M) y[(size_t)m * N + n] = t;
+        } else if (lane == 0) {
+            part[warp][m] = t;
+        }
+    }
+    if (WPC > 1) {
+        __syncthreads();
+        if (kw == 0 && lane < MR && lane < M && valid) {
+            float t = part[warp][lane];
+#pragma unroll
+            for (int x = 1; x < WPC; ++x) t += part[warp + x][lane];
+            y[(size_t)lane * N + n] = t;
+        }
     }
 }
 
@@ -1333,11 +1393,20 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
         }
     }
     if (M <= 8 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
-        const int grid = (N + 7) / 8;
-        if (M == 1) gemv_bf16_kernel<1><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
-        else if (M == 2) gemv_bf16_kernel<2><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
-        else if (M <= 4) gemv_bf16_kernel<4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
-        else gemv_bf16_kernel<8><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+        // warps per column by N alone: a row's result must not depend on what else the step holds
+        const int wpc = N >= 1184 ? 1 : N >= 592 ? 2 : 4;
+        const int grid = (N * wpc + 7) / 8;
+#define SMOL_GEMV(MR)                                                                                   \
+        do {                                                                                            \
+            if (wpc == 1) gemv_bf16_kernel<MR, 1><<<grid, 256, 0, st>>>(a, w, y, M, N, K);              \
+            else if (wpc == 2) gemv_bf16_kernel<MR, 2><<<grid, 256, 0, st>>>(a, w, y, M, N, K);         \
+            else gemv_bf16_kernel<MR, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);                       \
+        } while (0)
+        if (M == 1) SMOL_GEMV(1);
+        else if (M == 2) SMOL_GEMV(2);
+        else if (M <= 4) SMOL_GEMV(4);
+        else SMOL_GEMV(8);
+#undef SMOL_GEMV
     } else if (M <= 32) {
         dim3 grid((N + 31) / 32, (M + 31) / 32);
         gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 32 x 32

@@ -221,6 +221,7 @@ def test_linear_kernels_against_torch():
     modelb, _, _ = engine_and_oracle(config([attn(ff=0)]), seed=9, dtype=BF16)
     g = torch.Generator(device="cuda").manual_seed(0)
     for M, N, K in ((1, 200, 72), (5, 33, 40), (17, 64, 256), (70, 130, 100), (300, 96, 35), (129, 257, 64),
+                    (3, 700, 512), (8, 1300, 264), (2, 768, 4608), (4, 100, 8),      # few rows: 2, 1, 2 and 4 warps per column
                     (260, 333, 72), (515, 96, 64), (1024, 768, 256), (300, 100, 136), (257, 97, 1000)):      # 257 rows and more: tcgen05 tiles
         a = torch.randn(M, K, device="cuda", generator=g)
         w = torch.randn(N, K, device="cuda", generator=g)

@@ -93,12 +93,52 @@ __global__ void norm_rows_kernel(const float* __restrict__ x, const int32_t* __r
 // End of a sublayer fused with the start of the next one:
 //   x <- x + ls * (y / rms(y) * (1 + wb));   hn <- x / rms(x) * (1 + wn)     (wn == nullptr: no next norm)
 // One block per row; the new row is kept in shared memory between the two passes.
+constexpr int kRowRegs = 8;   // add_norm keeps a row in registers when it has at most 8 elements per thread
+
 template <class T>
 __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
                                 const float* __restrict__ ls, const float* __restrict__ wn, float eps, int D, T* __restrict__ hn) {
     extern __shared__ float row[];
     __shared__ float red[33];
     const size_t o = (size_t)blockIdx.x * D;
+    if (D <= (int)blockDim.x * kRowRegs) {
+        // every operand is loaded before the first reduction: one round of global-memory latency for the whole kernel
+        float yv[kRowRegs], xv[kRowRegs], lv[kRowRegs], bv[kRowRegs], nv[kRowRegs];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            const bool in = c < D;
+            yv[i] = in ? y[o + c] : 0.0f;
+            xv[i] = in ? x[o + c] : 0.0f;
+            lv[i] = in ? ls[c] : 0.0f;
+            bv[i] = in ? wb[c] : 0.0f;
+            nv[i] = (in && wn) ? wn[c] : 0.0f;
+            ss += yv[i] * yv[i];
+        }
+        ss = block_sum(ss, red);
+        const float r = 1.0f / sqrtf(ss / (float)D + eps);
+        float s2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            const float v = xv[i] + lv[i] * (yv[i] * r * (1.0f + bv[i]));
+            xv[i] = v;
+            if (c < D) {
+                x[o + c] = v;
+                s2 += v * v;
+            }
+        }
+        if (!wn) return;
+        s2 = block_sum(s2, red);
+        const float r2 = 1.0f / sqrtf(s2 / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < D) hn[o + c] = from_f<T>(xv[i] * r2 * (1.0f + nv[i]));
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y[o + c]; ss += v * v; }
     ss = block_sum(ss, red);

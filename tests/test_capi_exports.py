@@ -56,7 +56,7 @@ def test_lm_library_exports_every_declared_symbol_and_validates_on_create():
     lib.smol_lm_destroy(h)
     layers[0].kv_heads = 3
     assert lib.smol_lm_create(ctypes.byref(cfg), layers, runs, ctypes.byref(h)) == -1
-    layers[0].kv_heads, layers[1].dim = 2, 160
+    layers[0].kv_heads, layers[1].dim = 2, 272
     assert lib.smol_lm_create(ctypes.byref(cfg), layers, runs, ctypes.byref(h)) == -4
 
 

@@ -57,6 +57,21 @@ def test_each_mechanism_alone(layers, dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_wide_residual_rows(dtype):
+    """A width beyond what the norm kernels keep in registers (their shared-memory form), prompt and decoding."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([attn(heads=2, kv_heads=1, dim=16, vdim=16, ff=40), delta(heads=1, dim=16, ff=0)], vocab=43, width=2120)
+    model, orc, _ = engine_and_oracle(cfg, seed=12, dtype=dtype)
+    toks = tokens(21, 43, 40)
+    want = orc.forward(toks)
+    b = TokenBatcher(model)
+    got = torch.cat([b.feed([("w", toks[:12], list(range(12)))])] + [b.feed([("w", [t], [0])]) for t in toks[12:]])
+    b.close()
+    assert rel_err(got, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
 def test_every_layer_run_of_a_looped_hybrid(dtype):
     model, orc, _ = engine_and_oracle(MIXED, seed=2, dtype=dtype)
     toks = tokens(50, MIXED["vocab"], 1)

@@ -102,7 +102,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
     __shared__ float red[33];
     const size_t o = (size_t)blockIdx.x * D;
     if (D <= (int)blockDim.x * kRowRegs) {
-        // every operand is loaded before the first reduction: one round of global-memory latency for the whole kernel
+        // every operand is loaded before the first reduction: the kernel waits for global memory once
         float yv[kRowRegs], xv[kRowRegs], lv[kRowRegs], bv[kRowRegs], nv[kRowRegs];
         float ss = 0.0f;
 #pragma unroll

@@ -736,22 +736,36 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
     const int t = t0 + r, pos = A.tok_pos[t];
     const int ns = pos / A.split_len + 1;
     const float* src = A.part + ((size_t)x * A.H + h) * A.n_splits * (A.dv + 2);
-    float M = A.sink[h];
-    for (int z = 0; z < ns; ++z) M = fmaxf(M, src[(size_t)z * (A.dv + 2)]);
-    float l = expf(A.sink[h] - M);
+    // lanes take the ranges' maxima and weights side by side; the value columns are then summed range by range with the
+    // weights handed on by shuffles, so that no load waits for an earlier one
+    const float sink = A.sink[h];
+    float M = sink;
+    for (int z = lane; z < ns; z += 32) M = fmaxf(M, src[(size_t)z * (A.dv + 2)]);
+    M = warp_max(M);
+    float l = 0.0f;
     float o[kAttnMaxV];
 #pragma unroll
     for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
-    for (int z = 0; z < ns; ++z) {
-        const float* p = src + (size_t)z * (A.dv + 2);
-        const float w = expf(p[0] - M);
-        l = fmaf(p[1], w, l);
+    for (int z0 = 0; z0 < ns; z0 += 32) {
+        const int z = z0 + lane, cnt = min(32, ns - z0);
+        float wz = 0.0f;
+        if (z < ns) {
+            const float* p = src + (size_t)z * (A.dv + 2);
+            wz = expf(p[0] - M);
+            l = fmaf(p[1], wz, l);
+        }
+#pragma unroll 4
+        for (int i = 0; i < cnt; ++i) {
+            const float w = __shfl_sync(0xffffffffu, wz, i);
+            const float* p = src + (size_t)(z0 + i) * (A.dv + 2) + 2;
 #pragma unroll
-        for (int e = 0; e < kAttnMaxV; ++e) {
-            const int c = lane + e * 32;
-            if (c < A.dv) o[e] = fmaf(p[2 + c], w, o[e]);
+            for (int e = 0; e < kAttnMaxV; ++e) {
+                const int c = lane + e * 32;
+                if (c < A.dv) o[e] = fmaf(p[c], w, o[e]);
+            }
         }
     }
+    l = warp_sum(l) + expf(sink - M);
     const float inv = 1.0f / l;
     const float* gate = A.proj + (size_t)t * A.n_in + A.H * A.d + A.G * A.d + A.G * A.dv + h * A.dv;
 #pragma unroll

@@ -1,7 +1,8 @@
 /*
  * smoltts_b200 -- C ABI of the hybrid language-model engine (libsmoltts_b200_lm.so): decoder-only models whose layers
- * mix tokens either by softmax attention over a paged key/value pool or by a recurrent matrix state kept in per-sequence
- * slots.  Same conventions as smoltts_b200.h: plain C types, every pointer is a DEVICE pointer owned by the caller unless
+ * mix tokens either by softmax attention over a paged key/value pool (keys and values themselves, or one compressed
+ * latent per position from which every head's keys and values follow) or by a recurrent matrix state kept in
+ * per-sequence slots; feed-forwards are dense or a routed mixture of small experts.  Same conventions as smoltts_b200.h: plain C types, every pointer is a DEVICE pointer owned by the caller unless
  * said otherwise, every compute call is asynchronous on the given cudaStream_t (passed as void*), no allocation after
  * create, 0 / negative SMOL_ERR_* return codes with smol_lm_last_error().
  *
@@ -22,13 +23,32 @@
 extern "C" {
 #endif
 
-#define SMOL_LM_ABI_VERSION 1
+#define SMOL_LM_ABI_VERSION 2
 
 enum { SMOL_LM_BF16 = 0, SMOL_LM_F32 = 1 };
 /* token mixers */
-enum { SMOL_LM_MIX_SINK_ATTENTION = 0, SMOL_LM_MIX_GENERAL_DELTA = 1 };
+enum {
+    SMOL_LM_MIX_SINK_ATTENTION = 0,    /* grouped-query attention, q/k norms, distance penalty, softmax sink, per-channel gate */
+    SMOL_LM_MIX_GENERAL_DELTA = 1,     /* generalized delta rule, state [dim, dim] per head */
+    SMOL_LM_MIX_LATENT_ATTENTION = 2,  /* attention through a cached latent: queries and keys/values are low-rank, part of each
+                                          head's query/key is rotated by position, one gate per head */
+    SMOL_LM_MIX_GATED_LINEAR = 3       /* linear attention with a decay per key channel, state [dim, vdim] per head */
+};
 /* feed-forward kinds */
-enum { SMOL_LM_MLP_NONE = 0, SMOL_LM_MLP_POLYNORM = 1 };
+enum {
+    SMOL_LM_MLP_NONE = 0,
+    SMOL_LM_MLP_POLYNORM = 1,          /* up, PolyNorm, down */
+    SMOL_LM_MLP_GATED = 2,             /* down(act(gate) * up) */
+    SMOL_LM_MLP_EXPERTS = 3            /* routed mixture of gated experts, some router outputs standing for the input itself */
+};
+/* activations of the gated feed-forwards */
+enum { SMOL_LM_ACT_GELU_TANH = 0, SMOL_LM_ACT_SILU = 1 };
+/* how a layer wraps its sublayers */
+enum {
+    SMOL_LM_BLOCK_SANDWICH = 0,        /* x += ls * norm_b(sublayer(norm_a(x))): norms with one-plus weight vectors, layer scales */
+    SMOL_LM_BLOCK_POSTNORM = 1         /* x = g * rms_divide(alpha * x + sublayer(x)): one gain per norm; after each layer the
+                                          stream becomes a weighted sum of the embedding output and every layer's result */
+};
 
 /* One layer: sizes, constants and weights.  Matrices (`const void*`) have the engine's element type and are [out, in]
  * row-major; vectors (`const float*`) are always fp32. */
@@ -54,6 +74,29 @@ typedef struct SmolLmLayer {
     const float *decay_w2, *decay_bias;             /* recurrent: second decay matrix TRANSPOSED, [rank, heads * dim] fp32; [heads * dim] */
     const float *out_norm;                          /* recurrent: plain weight after the per-head RMS division [heads * dim] */
     const float *act;                               /* PolyNorm coefficients a, b, c, e */
+    /* --- latent attention, gated linear recurrence, gated and routed feed-forwards --- */
+    int32_t rot_dim;          /* latent attention: rotated query/key coordinates per head (after the `dim` unrotated ones) */
+    int32_t q_rank, kv_rank;  /* latent attention: sizes of the query latent and of the cached key/value latent */
+    int32_t mlp_act;          /* SMOL_LM_ACT_* of a gated feed-forward or of the experts */
+    int32_t n_experts;        /* routed: experts with weights */
+    int32_t n_identity;       /* routed: further router outputs whose "expert" returns its input */
+    int32_t top_k;            /* routed: router outputs used per token */
+    int32_t n_groups, keep_groups;  /* routed: outputs form n_groups equal groups of neighbours, chosen from the best keep_groups */
+    float rot_base;           /* rotation angle of pair i at position p: p * rot_base^(-2i / rot_dim) */
+    float decay_tau;          /* gated linear: decay = sigmoid(z)^(1 / decay_tau) */
+    float router_scale;       /* routed: multiplies the normalised weights */
+    /* latent attention: w_in rows are query-latent [q_rank] | key/value latent [kv_rank] | shared rotated key [rot_dim] | gate [heads];
+     * gated linear: w_in rows are q | k [heads*dim each] | v | gate [heads*vdim each] | decay-inner [rank], and score_scale multiplies q;
+     * decay_w2 / decay_bias are used as in the delta rule (second decay matrix transposed, fp32) */
+    const void* w_q_up;       /* latent attention: [heads * (dim + rot_dim), q_rank] */
+    const void* w_k_up_t;     /* latent attention: per head the key expansion TRANSPOSED, [heads][kv_rank][dim] */
+    const void* w_v_up;       /* latent attention: [heads * vdim, kv_rank] */
+    const float *q_lat_norm, *kv_lat_norm;   /* latent attention: plain RMS-norm weights [q_rank], [kv_rank] */
+    const void* w_experts_in; /* routed: [n_experts][2 * ff][width], gate rows then up rows; gated: w_up holds [2 * ff][width] likewise */
+    const void* w_experts_out;/* routed: [n_experts][width][ff] */
+    const float* w_router;    /* routed: [n_experts + n_identity][width] fp32 */
+    const float* route_bias;  /* routed: added to the scores for the choice only [n_experts + n_identity] */
+    const float* depth_mix;   /* post-norm block: weights of the embedding output and of every layer result so far [run + 2] */
 } SmolLmLayer;
 
 typedef struct SmolLmConfig {
@@ -68,12 +111,16 @@ typedef struct SmolLmConfig {
     int32_t max_context;      /* most positions one sequence may hold (sizes the scratch of the few-token attention path) */
     int32_t use_graph;        /* 1: steps of few tokens (decoding) are captured once per shape into a CUDA graph and replayed */
     float embed_scale, norm_eps;
+    int32_t block;            /* SMOL_LM_BLOCK_* */
+    float residual_alpha;     /* post-norm block: multiplies the stream before the sublayer's output is added */
+    float logit_scale;        /* multiplies the logits */
 } SmolLmConfig;
 
 typedef struct SmolLmGlobals {
     const void* embed;        /* [vocab, width] */
     const void* head;         /* [vocab, width] */
-    const float* final_norm;  /* [width] one-plus weight */
+    const float* final_norm;  /* sandwich block: [width] one-plus weight; post-norm block: one gain */
+    const float* embed_norm;  /* post-norm block: one gain of the norm after the embedding */
 } SmolLmGlobals;
 
 /* A ragged batch.  All arrays live on the device. */
@@ -103,7 +150,7 @@ const char* smol_lm_last_error(void);
 int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers, const int32_t* run_layer, SmolLm** out);
 void smol_lm_destroy(SmolLm* m);
 
-size_t smol_lm_page_bytes(const SmolLm* m);       /* one page: page_size positions of every attention run's keys and values */
+size_t smol_lm_page_bytes(const SmolLm* m);       /* one page: page_size positions of every attention run's keys and values (or latents) */
 size_t smol_lm_slot_bytes(const SmolLm* m);       /* one slot: the fp32 matrix states of every recurrent run */
 size_t smol_lm_workspace_bytes(const SmolLm* m);
 

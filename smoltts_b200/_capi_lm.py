@@ -11,7 +11,7 @@ import os
 from . import build as _build
 from ._errors import SMOL_OK, SmolError
 
-SMOL_LM_ABI_VERSION = 1
+SMOL_LM_ABI_VERSION = 2
 SMOL_LM_BF16, SMOL_LM_F32 = 0, 1
 
 
@@ -20,16 +20,21 @@ class SmolLmLayer(C.Structure):
         (n, C.c_float) for n in ("score_scale", "decay_coef", "unit_eps")] + [
         (n, C.c_void_p) for n in ("w_in", "w_out", "w_up", "w_down", "norm1", "norm1b", "norm2", "norm2b", "ls1", "ls2",
                                   "q_norm", "k_norm", "dist_r1", "dist_r2", "sink", "rate_bias", "decay_w2", "decay_bias",
-                                  "out_norm", "act")]
+                                  "out_norm", "act")] + [
+        (n, C.c_int32) for n in ("rot_dim", "q_rank", "kv_rank", "mlp_act", "n_experts", "n_identity", "top_k", "n_groups", "keep_groups")] + [
+        (n, C.c_float) for n in ("rot_base", "decay_tau", "router_scale")] + [
+        (n, C.c_void_p) for n in ("w_q_up", "w_k_up_t", "w_v_up", "q_lat_norm", "kv_lat_norm", "w_experts_in", "w_experts_out", "w_router",
+                                  "route_bias", "depth_mix")]
 
 
 class SmolLmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
-                                         "max_step_seqs", "max_want", "max_context", "use_graph")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)]
+                                         "max_step_seqs", "max_want", "max_context", "use_graph")] + [
+        ("embed_scale", C.c_float), ("norm_eps", C.c_float), ("block", C.c_int32), ("residual_alpha", C.c_float), ("logit_scale", C.c_float)]
 
 
 class SmolLmGlobals(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("embed", "head", "final_norm")]
+    _fields_ = [(n, C.c_void_p) for n in ("embed", "head", "final_norm", "embed_norm")]
 
 
 class SmolLmStep(C.Structure):

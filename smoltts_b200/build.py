@@ -27,8 +27,8 @@ LM_LIB_PATH = os.path.join(LIB_DIR, "libsmoltts_b200_lm.so")
 TARGETS = {
     "core": (LIB_PATH, STAMP, SOURCES, HEADERS),
     "lm": (LM_LIB_PATH, os.path.join(LIB_DIR, "build_lm.stamp"), ["lm_kernels.cu"],
-           ["common.cuh", "dev_model.h", "sampler.cuh", "umma.cuh", "tmap_host.h", os.path.join("..", "..", "include", "smoltts_b200.h"),
-            os.path.join("..", "..", "include", "smoltts_b200_lm.h")]),
+           ["common.cuh", "dev_model.h", "sampler.cuh", "umma.cuh", "tmap_host.h", "lm_mechanisms.cuh",
+            os.path.join("..", "..", "include", "smoltts_b200.h"), os.path.join("..", "..", "include", "smoltts_b200_lm.h")]),
 }
 
 NVCC_FLAGS = [

@@ -221,14 +221,51 @@ __global__ void polynorm_kernel(const float* __restrict__ z, const float* __rest
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Where the operands of a matrix product live beyond the plain case (a [M, K], w [N, K], y [M, N], all contiguous).
+//  - lda / ldy: row strides of a and y; blockIdx.z is a batch index with the strides sa / sw / sy (one product per head).
+//  - grouped rows (tile_group != nullptr): the rows are sorted by group (expert), group g owning rows seg[g] .. seg[g+1]-1
+//    and the weight matrix w + g * sw; blockIdx.y walks a tile table built on the device (tiles beyond *n_tiles leave at
+//    once), and row r of the sorted order reads a's row gather[r] / gather_div (gather == nullptr: row r itself).
+struct GemmIo {
+    int lda, ldy;
+    long long sa, sw, sy;
+    const int32_t *tile_group, *tile_row0, *seg, *n_tiles, *gather;
+    int gather_div;
+};
+constexpr int kGroupTile = 32;     // rows per tile of a grouped product (the tile table is built for this height)
+static GemmIo plain_io(int K, int N) {
+    GemmIo io;
+    io.lda = K; io.ldy = N; io.sa = io.sw = io.sy = 0;
+    io.tile_group = io.tile_row0 = io.seg = io.n_tiles = io.gather = nullptr;
+    io.gather_div = 1;
+    return io;
+}
+
 // Matrix product, fp32: y[M, N] = a[M, K] . w[N, K]^T with plain FMAs, k ascending (the result of a row does not depend on M).
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ w,
-                                                                        float* __restrict__ y, int M, int N, int K) {
+                                                                        float* __restrict__ y, int M, int N, int K, const GemmIo io) {
     constexpr int NT = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 1];
     __shared__ float Ws[BK][BN + 1];
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    __shared__ long long arow[BM];
+    int m0 = blockIdx.y * BM;
+    const int n0 = blockIdx.x * BN;
+    a += blockIdx.z * io.sa;
+    w += blockIdx.z * io.sw;
+    y += blockIdx.z * io.sy;
+    if (io.tile_group) {
+        if ((int)blockIdx.y >= *io.n_tiles) return;
+        const int g = io.tile_group[blockIdx.y];
+        m0 = io.tile_row0[blockIdx.y];
+        M = io.seg[g + 1];
+        w += (long long)g * io.sw;
+    }
+    for (int r = threadIdx.x; r < BM; r += NT) {
+        const int m = m0 + r;
+        arow[r] = m < M ? (long long)(io.gather ? io.gather[m] / io.gather_div : m) * io.lda : -1;
+    }
+    __syncthreads();
     const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
     float acc[TM][TN];
 #pragma unroll
@@ -238,7 +275,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_f32_kernel(const f
     for (int k0 = 0; k0 < K; k0 += BK) {
         for (int i = threadIdx.x; i < BM * BK; i += NT) {
             const int r = i / BK, c = i % BK;
-            As[c][r] = (m0 + r < M && k0 + c < K) ? a[(size_t)(m0 + r) * K + k0 + c] : 0.0f;
+            As[c][r] = (arow[r] >= 0 && k0 + c < K) ? a[arow[r] + k0 + c] : 0.0f;
         }
         for (int i = threadIdx.x; i < BN * BK; i += NT) {
             const int r = i / BK, c = i % BK;
@@ -264,7 +301,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_f32_kernel(const f
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int m = m0 + ty * TM + i, n = n0 + tx + j * (BN / TN);
-            if (m < M && n < N) y[(size_t)m * N + n] = acc[i][j];
+            if (m < M && n < N) y[(size_t)m * io.ldy + n] = acc[i][j];
         }
 }
 
@@ -273,14 +310,16 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_f32_kernel(const f
 constexpr int kGemmBK = 32;
 constexpr int kGemmLd = kGemmBK + 8;   // 80-byte rows: fragment loads hit 32 distinct banks
 
+// off[i]: element offset of the i-th row this thread fetches (negative: a row outside the matrix, read as zeros)
 template <int ROWS>
-__device__ __forceinline__ void gemm_fetch(const bf16* __restrict__ src, int r0, int R, int K, int k0, bool vec, uint4 (&reg)[ROWS * 4 / 128]) {
+__device__ __forceinline__ void gemm_fetch(const bf16* __restrict__ src, const long long (&off)[ROWS * 4 / 128], int K, int k0, bool vec,
+                                           uint4 (&reg)[ROWS * 4 / 128]) {
 #pragma unroll
     for (int i = 0; i < ROWS * 4 / 128; ++i) {
-        const int id = threadIdx.x + i * 128, r = id >> 2, c = (id & 3) * 8;
+        const int c = (threadIdx.x & 3) * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r0 + r < R) {
-            const bf16* p = src + (size_t)(r0 + r) * K + k0 + c;
+        if (off[i] >= 0) {
+            const bf16* p = src + off[i] + k0 + c;
             if (vec && k0 + c + 8 <= K) {
                 v = *reinterpret_cast<const uint4*>(p);
             } else {
@@ -303,18 +342,29 @@ __device__ __forceinline__ void gemm_stash(bf16* dst, const uint4 (&reg)[ROWS * 
     }
 }
 
+// `vec`: every row of a and w starts on a 16-byte boundary and K is a multiple of 8 (whole 16-byte pieces).
 template <int WR, int WC, int MT, int NT>
 __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ y,
-                                                        int M, int N, int K) {
+                                                        int M, int N, int K, const GemmIo io, const bool vec) {
     static_assert(WR * WC == 4, "four warps");
     constexpr int BM = WR * MT * 16, BN = WC * NT * 8;
     static_assert(BM % 32 == 0 && BN % 32 == 0, "tile rows are fetched 32 at a time");
     __shared__ __align__(16) bf16 As[2][BM * kGemmLd];
     __shared__ __align__(16) bf16 Ws[2][BN * kGemmLd];
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    int m0 = blockIdx.y * BM;
+    const int n0 = blockIdx.x * BN;
+    a += blockIdx.z * io.sa;
+    w += blockIdx.z * io.sw;
+    y += blockIdx.z * io.sy;
+    if (io.tile_group) {
+        if ((int)blockIdx.y >= *io.n_tiles) return;
+        const int g = io.tile_group[blockIdx.y];
+        m0 = io.tile_row0[blockIdx.y];
+        M = io.seg[g + 1];
+        w += (long long)g * io.sw;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     const int wm = (warp / WC) * MT * 16, wn = (warp % WC) * NT * 8;
-    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);
     float acc[MT][NT][4];
 #pragma unroll
     for (int i = 0; i < MT; ++i)
@@ -323,8 +373,19 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
     uint4 ra[BM * 4 / 128], rw[BN * 4 / 128];
-    gemm_fetch<BM>(a, m0, M, K, 0, vec, ra);
-    gemm_fetch<BN>(w, n0, N, K, 0, vec, rw);
+    long long oa[BM * 4 / 128], ow[BN * 4 / 128];
+#pragma unroll
+    for (int i = 0; i < BM * 4 / 128; ++i) {
+        const int m = m0 + ((threadIdx.x + i * 128) >> 2);
+        oa[i] = m < M ? (long long)(io.gather ? io.gather[m] / io.gather_div : m) * io.lda : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < BN * 4 / 128; ++i) {
+        const int n = n0 + ((threadIdx.x + i * 128) >> 2);
+        ow[i] = n < N ? (long long)n * K : -1;
+    }
+    gemm_fetch<BM>(a, oa, K, 0, vec, ra);
+    gemm_fetch<BN>(w, ow, K, 0, vec, rw);
     gemm_stash<BM>(As[0], ra);
     gemm_stash<BN>(Ws[0], rw);
     __syncthreads();
@@ -332,8 +393,8 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
     for (int s = 0; s < steps; ++s) {
         const int cur = s & 1;
         if (s + 1 < steps) {
-            gemm_fetch<BM>(a, m0, M, K, (s + 1) * kGemmBK, vec, ra);
-            gemm_fetch<BN>(w, n0, N, K, (s + 1) * kGemmBK, vec, rw);
+            gemm_fetch<BM>(a, oa, K, (s + 1) * kGemmBK, vec, ra);
+            gemm_fetch<BN>(w, ow, K, (s + 1) * kGemmBK, vec, rw);
         }
 #pragma unroll
         for (int kk = 0; kk < kGemmBK; kk += 16) {
@@ -371,7 +432,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int mm = m + (e >> 1) * 8, nn = n + (e & 1);
-                if (mm < M && nn < N) y[(size_t)mm * N + nn] = acc[i][j][e];
+                if (mm < M && nn < N) y[(size_t)mm * io.ldy + nn] = acc[i][j][e];
             }
         }
 }
@@ -472,13 +533,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Attention with a sink.  proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv].
+// Softmax attention over the paged pool.  A cached position holds, per key/value head, a key row of d elements (row
+// stride k_ld) and a value row of dv elements (row stride v_ld); with v_in_k the value is the first dv elements of the key
+// row (a latent that serves as both).  Optional per head: a distance penalty r1 ln(1 + r2 (i - j)) taken off the score
+// (r1 == nullptr: none) and a key-less sink logit in the softmax denominator (sink == nullptr: none).  The output is
+// multiplied by sigmoid(proj[t][gate_off + h * gate_ld + c * gate_step]): a gate per channel or (gate_step 0) per head.
+// Sink attention's proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv].
 struct AttnArgs {
     const float* proj;
     int n_in;
     const int32_t *tok_seq, *tok_pos, *block_table;
     int max_pages, page_size, n_pages;
     size_t page_elems, k_off, v_off;   // element offsets of this run's keys / values inside a page
+    int k_ld, v_ld, v_in_k;
+    size_t gate_off;
+    int gate_ld, gate_step;
     int H, G, d, dv;
     float scale, eps;
     const float *q_norm, *k_norm, *r1, *r2, *sink;
@@ -537,9 +606,13 @@ __global__ void attn_prep_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __re
 // memory), the round's softmax weights are shared by shuffles and every lane accumulates dv / 32 output columns.
 // The sink enters as the initial state of the running softmax: maximum = sink, denominator = 1, no value.
 constexpr int kAttnWarps = 4;
-constexpr int kAttnMaxV = 8;   // value size up to 256
+constexpr int kAttnMaxV = 16;  // value size up to 512; the kernels are built for 8 (up to 256) and 16 lanes' worth of columns
 
-template <class T>
+__device__ __forceinline__ float attn_gate(const AttnArgs& A, size_t t, int h, int c) {
+    return sigmoidf_(A.proj[t * A.n_in + A.gate_off + (size_t)h * A.gate_ld + (size_t)c * A.gate_step]);
+}
+
+template <class T, int MAXV>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool,
                                                                T* __restrict__ out) {
     extern __shared__ float qs_all[];
@@ -553,11 +626,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
     __syncwarp();
     const int pos = A.tok_pos[t];
     const int32_t* bt = A.block_table + (size_t)A.tok_seq[t] * A.max_pages;
-    const float r1 = A.r1[h], r2 = A.r2[h];
-    float m = A.sink[h], l = 1.0f;
-    float o[kAttnMaxV];
+    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f;
+    float m = A.sink ? A.sink[h] : -INFINITY, l = A.sink ? 1.0f : 0.0f;
+    float o[MAXV];
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+    for (int e = 0; e < MAXV; ++e) o[e] = 0.0f;
     for (int j0 = 0; j0 <= pos; j0 += 32) {
         const int j = j0 + lane;
         float s = -INFINITY;
@@ -565,36 +638,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
         if (j <= pos) {
             const int page = bt[j / A.page_size], in_pg = j % A.page_size;
             const T* base = pool + (size_t)page * A.page_elems;
-            const T* k = base + A.k_off + ((size_t)g * A.page_size + in_pg) * A.d;
-            vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv;
+            const T* k = base + A.k_off + ((size_t)g * A.page_size + in_pg) * A.k_ld;
+            vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.v_ld;
             float dot = 0.0f;
             for (int c = 0; c < A.d; ++c) dot = fmaf(qs[c], to_f<T>(k[c]), dot);
-            s = dot * A.scale - r1 * log1pf(r2 * (float)(pos - j));
+            s = dot * A.scale;
+            if (A.r1) s -= r1 * log1pf(r2 * (float)(pos - j));
         }
-        const float mn = fmaxf(m, warp_max(s));
+        const float mn = fmaxf(m, warp_max(s));          // finite: lane 0 of every round holds a visible key
         const float p = (j <= pos) ? expf(s - mn) : 0.0f;
         const float corr = expf(m - mn);
         l = l * corr + warp_sum(p);
         m = mn;
 #pragma unroll
-        for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
+        for (int e = 0; e < MAXV; ++e) o[e] *= corr;
         const int cnt = min(32, pos - j0 + 1);
         for (int jj = 0; jj < cnt; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const T* vr = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(vrow), jj));
 #pragma unroll
-            for (int e = 0; e < kAttnMaxV; ++e) {
+            for (int e = 0; e < MAXV; ++e) {
                 const int c = lane + e * 32;
                 if (c < A.dv) o[e] = fmaf(pj, to_f<T>(vr[c]), o[e]);
             }
         }
     }
     const float inv = 1.0f / l;
-    const float* gate = A.proj + (size_t)t * A.n_in + A.H * A.d + A.G * A.d + A.G * A.dv + h * A.dv;
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) {
+    for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
-        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * sigmoidf_(gate[c]));
+        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
     }
 }
 
@@ -636,7 +709,7 @@ template <> __device__ __forceinline__ float key_dot<bf16>(const float* qs, cons
     return dot;
 }
 
-template <class T>
+template <class T, int MAXV>
 __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const T* __restrict__ qbuf, const T* __restrict__ pool) {
     // One block per (row, key/value head x group of up to 8 of its query heads, key range); one warp per query head.
     // 32 keys and values at a time are staged in shared memory (rows padded by 16 bytes: conflict-free row-per-lane
@@ -656,20 +729,22 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool active = hq < Gq;
     const int h = g * Gq + (active ? hq : 0);
-    const int ldk = A.d + kPad, ldv = A.dv + kPad;
+    const int ldk = A.d + kPad, ldv = A.v_in_k ? ldk : A.dv + kPad;
     float* qs = reinterpret_cast<float*>(sm_raw) + warp * A.d;
     float* ps = reinterpret_cast<float*>(sm_raw) + nwarp * A.d + warp * 32;
     T* Ks = reinterpret_cast<T*>(sm_raw + (((size_t)nwarp * (A.d + 32) * 4 + 15) / 16) * 16);
-    T* Vs = Ks + 32 * ldk;
+    T* Vs = A.v_in_k ? Ks : Ks + 32 * ldk;
     const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
     for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
-    const float r1 = A.r1[h], r2 = A.r2[h];
+    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f;
     float m = -INFINITY, l = 0.0f;
-    float o[kAttnMaxV];
+    float o[MAXV];
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
-    const bool kvec = (A.d * sizeof(T)) % 16 == 0, vvec = (A.dv * sizeof(T)) % 16 == 0;
-    const int kchunks = kvec ? A.d / kPad : A.d, vchunks = vvec ? A.dv / kPad : A.dv;
+    for (int e = 0; e < MAXV; ++e) o[e] = 0.0f;
+    // whole 16-byte pieces when every cached row starts on a 16-byte boundary (pages are 16-byte aligned)
+    const bool kvec = (A.d * sizeof(T)) % 16 == 0 && (A.k_ld * sizeof(T)) % 16 == 0 && (A.k_off * sizeof(T)) % 16 == 0;
+    const bool vvec = (A.dv * sizeof(T)) % 16 == 0 && (A.v_ld * sizeof(T)) % 16 == 0 && (A.v_off * sizeof(T)) % 16 == 0;
+    const int kchunks = kvec ? A.d / kPad : A.d, vchunks = A.v_in_k ? 0 : (vvec ? A.dv / kPad : A.dv);
     for (int j0 = j_lo; j0 <= j_hi; j0 += 32) {
         const int cnt = min(32, j_hi - j0 + 1);
         __syncthreads();
@@ -679,12 +754,12 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
             const T* base = pool + (size_t)bt[j / A.page_size] * A.page_elems;
             const size_t in_pg = (size_t)g * A.page_size + j % A.page_size;
             if (c < kchunks) {
-                const T* src = base + A.k_off + in_pg * A.d;
+                const T* src = base + A.k_off + in_pg * A.k_ld;
                 if (kvec) *reinterpret_cast<uint4*>(Ks + row * ldk + c * kPad) = *reinterpret_cast<const uint4*>(src + c * kPad);
                 else Ks[row * ldk + c] = src[c];
             } else {
                 const int cv = c - kchunks;
-                const T* src = base + A.v_off + in_pg * A.dv;
+                const T* src = base + A.v_off + in_pg * A.v_ld;
                 if (vvec) *reinterpret_cast<uint4*>(Vs + row * ldv + cv * kPad) = *reinterpret_cast<const uint4*>(src + cv * kPad);
                 else Vs[row * ldv + cv] = src[cv];
             }
@@ -693,7 +768,10 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
         if (!active) continue;
         const int j = j0 + lane;
         float sc = -INFINITY;
-        if (lane < cnt) sc = key_dot<T>(qs, Ks + lane * ldk, A.d) * A.scale - r1 * log1pf(r2 * (float)(pos - j));
+        if (lane < cnt) {
+            sc = key_dot<T>(qs, Ks + lane * ldk, A.d) * A.scale;
+            if (A.r1) sc -= r1 * log1pf(r2 * (float)(pos - j));
+        }
         const float mn = fmaxf(m, warp_max(sc));          // finite: lane 0 of every round holds a valid key
         const float p = lane < cnt ? expf(sc - mn) : 0.0f;
         const float corr = expf(m - mn);
@@ -702,11 +780,11 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
         ps[lane] = p;
         __syncwarp();
 #pragma unroll
-        for (int e = 0; e < kAttnMaxV; ++e) o[e] *= corr;
+        for (int e = 0; e < MAXV; ++e) o[e] *= corr;
         for (int jj = 0; jj < cnt; ++jj) {
             const float pj = ps[jj];
 #pragma unroll
-            for (int e = 0; e < kAttnMaxV; ++e) {
+            for (int e = 0; e < MAXV; ++e) {
                 const int c = lane + e * 32;
                 if (c < A.dv) o[e] = fmaf(pj, to_f<T>(Vs[jj * ldv + c]), o[e]);
             }
@@ -717,14 +795,14 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
     float* dst = A.part + (((size_t)blockIdx.x * A.H + h) * A.n_splits + blockIdx.z) * (A.dv + 2);
     if (lane == 0) { dst[0] = m; dst[1] = l; }
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) {
+    for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
         if (c < A.dv) dst[2 + c] = o[e];
     }
 }
 
 // One warp per (row, query head): merges the ranges; the sink enters here, once, with no value.
-template <class T>
+template <class T, int MAXV>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -738,14 +816,14 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
     const float* src = A.part + ((size_t)x * A.H + h) * A.n_splits * (A.dv + 2);
     // lanes take the ranges' maxima and weights side by side; the value columns are then summed range by range with the
     // weights handed on by shuffles, so that no load waits for an earlier one
-    const float sink = A.sink[h];
+    const float sink = A.sink ? A.sink[h] : -INFINITY;
     float M = sink;
     for (int z = lane; z < ns; z += 32) M = fmaxf(M, src[(size_t)z * (A.dv + 2)]);
     M = warp_max(M);
     float l = 0.0f;
-    float o[kAttnMaxV];
+    float o[MAXV];
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) o[e] = 0.0f;
+    for (int e = 0; e < MAXV; ++e) o[e] = 0.0f;
     for (int z0 = 0; z0 < ns; z0 += 32) {
         const int z = z0 + lane, cnt = min(32, ns - z0);
         float wz = 0.0f;
@@ -759,7 +837,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
             const float w = __shfl_sync(0xffffffffu, wz, i);
             const float* p = src + (size_t)(z0 + i) * (A.dv + 2) + 2;
 #pragma unroll
-            for (int e = 0; e < kAttnMaxV; ++e) {
+            for (int e = 0; e < MAXV; ++e) {
                 const int c = lane + e * 32;
                 if (c < A.dv) o[e] = fmaf(p[c], w, o[e]);
             }
@@ -767,11 +845,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
     }
     l = warp_sum(l) + expf(sink - M);
     const float inv = 1.0f / l;
-    const float* gate = A.proj + (size_t)t * A.n_in + A.H * A.d + A.G * A.d + A.G * A.dv + h * A.dv;
 #pragma unroll
-    for (int e = 0; e < kAttnMaxV; ++e) {
+    for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
-        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * sigmoidf_(gate[c]));
+        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
     }
 }
 
@@ -1233,6 +1310,8 @@ __global__ void __launch_bounds__(kThreads) lm_sample_kernel(const float* __rest
 }  // namespace lm
 }  // namespace smol
 
+#include "lm_mechanisms.cuh"
+
 // =====================================================================================================================
 // Host side
 using namespace smol::lm;
@@ -1253,6 +1332,7 @@ struct RunInfo {
     int layer;
     size_t k_off = 0, v_off = 0;   // attention: element offsets inside a page
     size_t state_off = 0;          // recurrent: float offset inside a slot
+    size_t freq_off = 0;           // latent attention: float offset of the run's rotation frequencies in the table
 };
 
 struct SmolLm {
@@ -1264,6 +1344,12 @@ struct SmolLm {
     int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
     // workspace carving (byte offsets)
     size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_oraw, o_q, o_hw, o_err, o_part, total;
+    // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
+    // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
+    size_t o_hist = 0, o_cq = 0, o_qf = 0, o_qt = 0, o_qlat = 0, o_freq = 0;
+    size_t o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
+    int max_cq = 0, max_qf = 0, max_qlat = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
+    std::vector<float> freq_table;
     int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
     char* ws = nullptr;
     void* pages = nullptr;
@@ -1287,6 +1373,8 @@ static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
 
 static int n_in_of(const SmolLmLayer& L) {
     if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim + L.heads * L.vdim;
+    if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) return L.q_rank + L.kv_rank + L.rot_dim + L.heads;
+    if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim + L.rank;
     return 5 * L.heads * L.dim + L.rank;
 }
 
@@ -1327,12 +1415,53 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->slot_floats += (size_t)L.heads * L.dim * L.dim;
             m->max_hd = std::max(m->max_hd, L.heads * L.dim);
             m->max_mix = std::max(m->max_mix, L.heads * L.dim);
+        } else if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
+            if (L.vdim < 1 || L.q_rank < 1 || L.kv_rank < 1 || L.rot_dim < 0 || L.rot_dim % 2) {
+                delete m;
+                return fail(SMOL_ERR_INVALID, "latent attention: vdim, q_rank, kv_rank must be positive and rot_dim even");
+            }
+            if (L.kv_rank > 32 * kAttnMaxV) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "latent attention: latent size above 512"); }
+            // a cached position: the latent, then the shared rotated key part; keys and values are the same row
+            r.k_off = r.v_off = m->page_elems;
+            m->page_elems += (size_t)cfg->page_size * (L.kv_rank + L.rot_dim);
+            r.freq_off = m->freq_table.size();
+            for (int i = 0; i < L.rot_dim / 2; ++i) m->freq_table.push_back((float)pow((double)L.rot_base, -2.0 * i / (double)L.rot_dim));
+            m->max_q = std::max(m->max_q, L.heads * (L.kv_rank + L.rot_dim));
+            m->max_heads = std::max(m->max_heads, L.heads);
+            m->max_vdim = std::max(m->max_vdim, L.kv_rank);
+            m->max_mix = std::max(m->max_mix, L.heads * std::max(L.kv_rank, L.vdim));
+            m->max_hd = std::max(m->max_hd, L.heads * L.vdim);
+            m->max_cq = std::max(m->max_cq, L.q_rank);
+            m->max_qf = std::max(m->max_qf, L.heads * (L.dim + L.rot_dim));
+            m->max_qlat = std::max(m->max_qlat, L.heads * L.kv_rank);
+        } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
+            if (L.dim > 256) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256"); }
+            if (L.rank < 1 || L.vdim < 1 || !(L.decay_tau > 0.0f)) { delete m; return fail(SMOL_ERR_INVALID, "gated linear: rank, vdim, tau must be positive"); }
+            r.state_off = m->slot_floats;
+            m->slot_floats += (size_t)L.heads * L.dim * L.vdim;
+            m->max_hd = std::max(m->max_hd, L.heads * std::max(L.dim, L.vdim));
+            m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
         } else {
             delete m;
             return fail(SMOL_ERR_UNSUPPORTED, "unknown mixer kind");
         }
-        if (L.mlp != SMOL_LM_MLP_NONE && L.mlp != SMOL_LM_MLP_POLYNORM) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "unknown feed-forward kind"); }
-        if (L.mlp != SMOL_LM_MLP_NONE) m->max_ff = std::max(m->max_ff, L.ff);
+        if (L.mlp < SMOL_LM_MLP_NONE || L.mlp > SMOL_LM_MLP_EXPERTS) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "unknown feed-forward kind"); }
+        if (L.mlp == SMOL_LM_MLP_POLYNORM) m->max_ff = std::max(m->max_ff, L.ff);
+        if (L.mlp == SMOL_LM_MLP_GATED || L.mlp == SMOL_LM_MLP_EXPERTS) {
+            if (L.ff < 1 || (L.mlp_act != SMOL_LM_ACT_GELU_TANH && L.mlp_act != SMOL_LM_ACT_SILU)) { delete m; return fail(SMOL_ERR_INVALID, "gated feed-forward: ff and activation"); }
+        }
+        if (L.mlp == SMOL_LM_MLP_GATED) m->max_ff = std::max(m->max_ff, 2 * L.ff);
+        if (L.mlp == SMOL_LM_MLP_EXPERTS) {
+            const int E = L.n_experts + L.n_identity;
+            if (L.n_experts < 0 || L.n_identity < 0 || E < 1 || E > kMaxRouted || L.top_k < 1 || L.top_k > kMaxTop || L.n_groups < 1 ||
+                E % L.n_groups != 0 || L.keep_groups < 1 || L.keep_groups > L.n_groups || L.top_k > L.keep_groups * (E / L.n_groups)) {
+                delete m;
+                return fail(SMOL_ERR_INVALID, "routed feed-forward: experts, groups and top do not fit each other");
+            }
+            m->max_top = std::max(m->max_top, L.top_k);
+            m->max_experts = std::max(m->max_experts, L.n_experts);
+            m->max_pair_ff = std::max(m->max_pair_ff, L.top_k * L.ff);
+        }
         m->max_in = std::max(m->max_in, n_in_of(L));
         m->runs.push_back(r);
     }
@@ -1361,6 +1490,28 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     m->split_len = std::max(64, ((ctx + 255) / 256 + 63) / 64 * 64);
     m->max_splits = ((ctx + m->split_len - 1) / m->split_len + 3) / 4 * 4;
     m->o_part = carve((size_t)cfg->max_step_seqs * kShortSeq * m->max_heads * m->max_splits * (m->max_vdim + 2) * 4);
+    if (cfg->block == SMOL_LM_BLOCK_POSTNORM) m->o_hist = carve((size_t)(cfg->n_runs + 1) * T * D * 4);
+    if (m->max_cq > 0) {
+        m->o_cq = carve(T * (size_t)m->max_cq * E);
+        m->o_qf = carve(T * (size_t)m->max_qf * 4);
+        m->o_qt = carve(T * (size_t)m->max_qf * E);
+        m->o_qlat = carve(T * (size_t)m->max_qlat * 4);
+        m->o_freq = carve(m->freq_table.size() * 4 + 4);
+    }
+    if (m->max_top > 0) {
+        const size_t pairs = T * (size_t)m->max_top;
+        m->o_sel_id = carve(pairs * 4);
+        m->o_sel_w = carve(pairs * 4);
+        m->o_perm = carve(pairs * 4);
+        m->o_slot_of = carve(pairs * 4);
+        m->o_seg = carve(((size_t)m->max_experts + 1) * 4);
+        m->o_tile_g = carve((pairs / kGroupTile + m->max_experts + 1) * 4);
+        m->o_tile_r = carve((pairs / kGroupTile + m->max_experts + 1) * 4);
+        m->o_ntiles = carve(4);
+        m->o_zp = carve(T * (size_t)m->max_pair_ff * 2 * 4);
+        m->o_actp = carve(T * (size_t)m->max_pair_ff * E);
+        m->o_yp = carve(pairs * D * 4);
+    }
     m->total = o;
     *out = m;
     return SMOL_OK;
@@ -1375,7 +1526,9 @@ extern "C" int32_t* smol_lm_error_word(SmolLm* m) { return (m && m->bound) ? rei
 
 template <int DK>
 static cudaError_t scan_attribute() {
-    return cudaFuncSetAttribute(delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * delta_buf_floats(DK) * sizeof(float)));
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * delta_buf_floats(DK) * sizeof(float)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * gla_buf_floats(DK) * sizeof(float)));
+    return e;
 }
 static constexpr int flash_smem_bytes(int DP) { return 4 * 64 * (DP + 8) * (int)sizeof(bf16); }
 
@@ -1386,7 +1539,8 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = scan_attribute<64>();
     if (e == cudaSuccess) e = scan_attribute<128>();
     if (e == cudaSuccess) e = scan_attribute<256>();
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128));
     return e;
 }
@@ -1412,6 +1566,9 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
     m->slots = static_cast<float*>(d_slots);
     m->n_pages = n_pages;
     m->n_slots = n_slots;
+    if (!m->freq_table.empty())
+        CU(cudaMemcpy(m->ws + m->o_freq, m->freq_table.data(), m->freq_table.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (m->cfg.block == SMOL_LM_BLOCK_POSTNORM && !g->embed_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: the post-norm block needs embed_norm");
     m->bound = true;
     return SMOL_OK;
 }
@@ -1420,14 +1577,55 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
 template <class T>
 static cudaError_t linear(SmolLm* m, const T* a, const T* w, float* y, int M, int N, int K, cudaStream_t st);
 
+// The general form: `io` places the operands (strides, a batch of `batch` products, or rows grouped by expert, in which
+// case M is the largest number of rows and `tiles` the size of the tile table's grid; tile_rows is the table's tile height).
+template <class T>
+static cudaError_t linear_ex(SmolLm* m, const T* a, const T* w, float* y, int M, int N, int K, const GemmIo& io, int batch, int tiles,
+                             cudaStream_t st);
+
+template <>
+cudaError_t linear_ex<float>(SmolLm* m, const float* a, const float* w, float* y, int M, int N, int K, const GemmIo& io, int batch, int tiles,
+                             cudaStream_t st) {
+    if (io.tile_group) {
+        dim3 grid((N + 63) / 64, tiles, 1);
+        gemm_f32_kernel<32, 64, 16, 2, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K, io);
+    } else if (M <= 16) {
+        dim3 grid((N + 63) / 64, (M + 15) / 16, batch);
+        gemm_f32_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K, io);
+    } else {
+        dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+        gemm_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K, io);
+    }
+    m->launches++;
+    return cudaGetLastError();
+}
+
 template <>
 cudaError_t linear<float>(SmolLm* m, const float* a, const float* w, float* y, int M, int N, int K, cudaStream_t st) {
-    if (M <= 16) {
-        dim3 grid((N + 63) / 64, (M + 15) / 16);
-        gemm_f32_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+    return linear_ex<float>(m, a, w, y, M, N, K, plain_io(K, N), 1, 0, st);
+}
+
+static bool io_vec(const void* a, const void* w, int K, const GemmIo& io) {
+    return K % 8 == 0 && io.lda % 8 == 0 && io.sa % 8 == 0 && io.sw % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0;
+}
+
+template <>
+cudaError_t linear_ex<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int M, int N, int K, const GemmIo& io, int batch, int tiles,
+                            cudaStream_t st) {
+    const bool vec = io_vec(a, w, K, io);
+    if (io.tile_group) {
+        dim3 grid((N + 31) / 32, tiles, 1);
+        gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K, io, vec);       // 32 x 32
+    } else if (M <= 32) {
+        dim3 grid((N + 31) / 32, (M + 31) / 32, batch);
+        gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K, io, vec);       // 32 x 32
+    } else if (M <= 256 || ((N + 63) / 64) * ((M + 127) / 128) * batch < 2 * 148) {      // 128-row tiles only when they still fill the GPU twice
+        dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+        gemm_bf16_kernel<2, 2, 2, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K, io, vec);       // 64 x 64
     } else {
-        dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, w, y, M, N, K);
+        dim3 grid((N + 63) / 64, (M + 127) / 128, batch);
+        gemm_bf16_kernel<2, 2, 4, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K, io, vec);       // 128 x 64
     }
     m->launches++;
     return cudaGetLastError();
@@ -1461,15 +1659,8 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
         else if (M <= 4) SMOL_GEMV(4);
         else SMOL_GEMV(8);
 #undef SMOL_GEMV
-    } else if (M <= 32) {
-        dim3 grid((N + 31) / 32, (M + 31) / 32);
-        gemm_bf16_kernel<1, 4, 2, 1><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 32 x 32
-    } else if (M <= 256 || ((N + 63) / 64) * ((M + 127) / 128) < 2 * 148) {      // 128-row tiles only when they still fill the GPU twice
-        dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_bf16_kernel<2, 2, 2, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 64 x 64
     } else {
-        dim3 grid((N + 63) / 64, (M + 127) / 128);
-        gemm_bf16_kernel<2, 2, 4, 4><<<grid, 128, 0, st>>>(a, w, y, M, N, K);       // 128 x 64
+        return linear_ex<bf16>(m, a, w, y, M, N, K, plain_io(K, N), 1, 0, st);
     }
     m->launches++;
     return cudaGetLastError();
@@ -1481,6 +1672,56 @@ static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec,
     constexpr int threads = delta_block_cols(DK) * delta_lanes(DK), groups = DK / delta_block_cols(DK);
     delta_scan_kernel<DK><<<n_seqs * A.H * groups, threads, 2 * delta_buf_floats(DK) * sizeof(float), st>>>(A, dec, u, au, pool, o_raw);
     return cudaGetLastError();
+}
+
+template <int DK>
+static cudaError_t launch_gla_scan(const GlaArgs& A, int n_seqs, const float* dec, float* pool, float* o_raw, cudaStream_t st) {
+    constexpr int CB = delta_block_cols(DK), threads = CB * delta_lanes(DK);
+    const int groups = (A.dv + CB - 1) / CB;
+    gla_scan_kernel<DK><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
+    return cudaGetLastError();
+}
+
+// The attention kernels over the rows of a step: prompt portions on the tensor-core form (bf16, `flash`) or the
+// warp-per-row form, sequences of few tokens on the split-range form.  `A` is complete except for the fields set here.
+template <class T, int MAXV>
+static void launch_attention(SmolLm* m, const SmolLmStep* s, AttnArgs& A, bool flash, const T* qbuf, const T* pool, T* mix, cudaStream_t st) {
+    const SmolLmConfig& c = m->cfg;
+    const int Tn = s->n_tokens;
+    A.seq_start = s->seq_start;
+    A.split_len = m->split_len;
+    A.short_rows = s->n_seqs * kShortSeq;
+    A.part = reinterpret_cast<float*>(m->ws + m->o_part);
+    const int min_n = s->min_seq_tokens > 0 ? s->min_seq_tokens : 1;
+    const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
+    const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
+    A.n_splits = std::min(m->max_splits, (max_pos / m->split_len + 4) / 4 * 4);
+    if (max_n > kShortSeq) {
+        if (flash) {
+            dim3 grid((max_n + 63) / 64, s->n_seqs, A.H);
+            const int hp = std::max(A.d, A.dv);
+            const bf16* qb = reinterpret_cast<const bf16*>(qbuf);
+            const bf16* pl = reinterpret_cast<const bf16*>(pool);
+            bf16* mx = reinterpret_cast<bf16*>(mix);
+            if (hp <= 32) attn_flash_kernel<32><<<grid, 128, flash_smem_bytes(32), st>>>(A, qb, pl, mx);
+            else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, flash_smem_bytes(64), st>>>(A, qb, pl, mx);
+            else attn_flash_kernel<128><<<grid, 128, flash_smem_bytes(128), st>>>(A, qb, pl, mx);
+        } else {
+            // every row, also those of short sequences
+            const int au = Tn * A.H;
+            attn_kernel<T, MAXV><<<(au + kAttnWarps - 1) / kAttnWarps, kAttnWarps * 32, kAttnWarps * A.d * sizeof(float), st>>>(A, qbuf, pool, mix);
+        }
+        m->launches += 1;
+    }
+    if (min_n <= kShortSeq && (flash || max_n <= kShortSeq)) {
+        const int Gq = A.H / A.G, nwarp = std::min(Gq, 8), groups = (Gq + nwarp - 1) / nwarp;
+        const int pad = 16 / (int)sizeof(T);
+        const size_t smem = ((size_t)nwarp * (A.d + 32) * 4 + 15) / 16 * 16 + (size_t)32 * (A.d + pad + (A.v_in_k ? 0 : A.dv + pad)) * sizeof(T);
+        dim3 grid(A.short_rows, A.G * groups, A.n_splits);
+        attn_split_kernel<T, MAXV><<<grid, nwarp * 32, smem, st>>>(A, qbuf, pool);
+        attn_merge_kernel<T, MAXV><<<(A.short_rows * A.H + 3) / 4, 128, 0, st>>>(A, mix);
+        m->launches += 2;
+    }
 }
 
 template <class T>
@@ -1501,11 +1742,20 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     T* qbuf = reinterpret_cast<T*>(m->ws + m->o_q);
     T* hw = reinterpret_cast<T*>(m->ws + m->o_hw);
     int32_t* err = reinterpret_cast<int32_t*>(m->ws + m->o_err);
+    float* hist = reinterpret_cast<float*>(m->ws + m->o_hist);
     T* pool = static_cast<T*>(m->pages);
     const int nthr = D >= 1024 ? 256 : 128;
+    const bool postnorm = c.block == SMOL_LM_BLOCK_POSTNORM;
+    const size_t hist_stride = (size_t)Tn * D;
+    constexpr bool kIsF32 = sizeof(T) == 4;
+    auto cast_grid = [](size_t n) { return (int)std::min<size_t>((n + 255) / 256, 148 * 8); };
 
-    embed_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
-                                              m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn);
+    if (postnorm) {
+        embed_gain_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), D, c.vocab, m->g.embed_norm, c.norm_eps, x, hist, hn);
+    } else {
+        embed_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
+                                                  m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn);
+    }
     m->launches++;
     for (size_t n = 0; n < m->runs.size(); ++n) {
         const RunInfo& R = m->runs[n];
@@ -1513,54 +1763,89 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         const int n_in = n_in_of(L);
         CU(linear<T>(m, hn, static_cast<const T*>(L.w_in), proj, Tn, n_in, D, st));
         int mix_cols;
-        if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
+        const T* mix_in = mix;          // what the output projection reads
+        if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
             AttnArgs A;
             A.proj = proj; A.n_in = n_in;
             A.tok_seq = s->tok_seq; A.tok_pos = s->tok_pos; A.block_table = s->block_table;
             A.max_pages = s->max_pages; A.page_size = c.page_size; A.n_pages = m->n_pages;
             A.page_elems = m->page_elems; A.k_off = R.k_off; A.v_off = R.v_off;
-            A.H = L.heads; A.G = L.kv_heads; A.d = L.dim; A.dv = L.vdim;
-            A.scale = L.score_scale; A.eps = c.norm_eps;
-            A.q_norm = L.q_norm; A.k_norm = L.k_norm; A.r1 = L.dist_r1; A.r2 = L.dist_r2; A.sink = L.sink;
+            A.H = L.heads; A.scale = L.score_scale; A.eps = c.norm_eps;
             A.n_tokens = Tn; A.err = err;
-            const int units = Tn * (L.heads + 2 * L.kv_heads);
-            attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
-            A.seq_start = s->seq_start;
-            A.split_len = m->split_len;
-            A.short_rows = s->n_seqs * kShortSeq;
-            A.part = reinterpret_cast<float*>(m->ws + m->o_part);
-            const int min_n = s->min_seq_tokens > 0 ? s->min_seq_tokens : 1;
-            const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
-            const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
-            A.n_splits = std::min(m->max_splits, (max_pos / m->split_len + 4) / 4 * 4);
-            const int hp = std::max(L.dim, L.vdim);
-            const bool flash = sizeof(T) == 2 && hp <= 128;
-            if (max_n > kShortSeq) {
-                if (flash) {
-                    dim3 grid((max_n + 63) / 64, s->n_seqs, L.heads);
-                    const bf16* qb = reinterpret_cast<const bf16*>(qbuf);
-                    const bf16* pl = reinterpret_cast<const bf16*>(pool);
-                    bf16* mx = reinterpret_cast<bf16*>(mix);
-                    if (hp <= 32) attn_flash_kernel<32><<<grid, 128, flash_smem_bytes(32), st>>>(A, qb, pl, mx);
-                    else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, flash_smem_bytes(64), st>>>(A, qb, pl, mx);
-                    else attn_flash_kernel<128><<<grid, 128, flash_smem_bytes(128), st>>>(A, qb, pl, mx);
-                } else {
-                    // every row, also those of short sequences
-                    const int au = Tn * L.heads;
-                    attn_kernel<T><<<(au + kAttnWarps - 1) / kAttnWarps, kAttnWarps * 32, kAttnWarps * L.dim * sizeof(float), st>>>(A, qbuf, pool, mix);
-                }
+            if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
+                A.G = L.kv_heads; A.d = L.dim; A.dv = L.vdim;
+                A.k_ld = L.dim; A.v_ld = L.vdim; A.v_in_k = 0;
+                A.gate_off = (size_t)L.heads * L.dim + (size_t)L.kv_heads * (L.dim + L.vdim); A.gate_ld = L.vdim; A.gate_step = 1;
+                A.q_norm = L.q_norm; A.k_norm = L.k_norm; A.r1 = L.dist_r1; A.r2 = L.dist_r2; A.sink = L.sink;
+                const int units = Tn * (L.heads + 2 * L.kv_heads);
+                attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
                 m->launches += 1;
-            }
-            if (min_n <= kShortSeq && (flash || max_n <= kShortSeq)) {
-                const int Gq = L.heads / L.kv_heads, nwarp = std::min(Gq, 8), groups = (Gq + nwarp - 1) / nwarp;
-                const int pad = 16 / (int)sizeof(T);
-                const size_t smem = ((size_t)nwarp * (L.dim + 32) * 4 + 15) / 16 * 16 + (size_t)32 * (L.dim + L.vdim + 2 * pad) * sizeof(T);
-                dim3 grid(A.short_rows, L.kv_heads * groups, A.n_splits);
-                attn_split_kernel<T><<<grid, nwarp * 32, smem, st>>>(A, qbuf, pool);
-                attn_merge_kernel<T><<<(A.short_rows * L.heads + 3) / 4, 128, 0, st>>>(A, mix);
+                const bool flash = sizeof(T) == 2 && std::max(L.dim, L.vdim) <= 128;
+                if (L.vdim <= 256) launch_attention<T, 8>(m, s, A, flash, qbuf, pool, mix, st);
+                else launch_attention<T, 16>(m, s, A, flash, qbuf, pool, mix, st);
+                mix_cols = L.heads * L.vdim;
+            } else {
+                const int dk = L.kv_rank + L.rot_dim, qw = L.dim + L.rot_dim;
+                T* cq = reinterpret_cast<T*>(m->ws + m->o_cq);
+                float* qf = reinterpret_cast<float*>(m->ws + m->o_qf);
+                T* qt = kIsF32 ? reinterpret_cast<T*>(qf) : reinterpret_cast<T*>(m->ws + m->o_qt);
+                float* qlat = reinterpret_cast<float*>(m->ws + m->o_qlat);
+                LatentArgs P;
+                P.proj = proj; P.n_in = n_in; P.q_rank = L.q_rank; P.kv_rank = L.kv_rank; P.rot = L.rot_dim; P.H = L.heads; P.d = L.dim;
+                P.eps = c.norm_eps; P.q_lat_norm = L.q_lat_norm; P.kv_lat_norm = L.kv_lat_norm;
+                P.freq = reinterpret_cast<const float*>(m->ws + m->o_freq) + R.freq_off;
+                P.tok_seq = s->tok_seq; P.tok_pos = s->tok_pos; P.block_table = s->block_table;
+                P.max_pages = s->max_pages; P.page_size = c.page_size; P.n_pages = m->n_pages; P.n_tokens = Tn;
+                P.page_elems = m->page_elems; P.k_off = R.k_off; P.err = err;
+                latent_prep_kernel<T><<<Tn, 128, 0, st>>>(P, cq, pool);
+                CU(linear<T>(m, cq, static_cast<const T*>(L.w_q_up), qf, Tn, L.heads * qw, L.q_rank, st));
+                if (!kIsF32) {
+                    cast_kernel<T><<<cast_grid((size_t)Tn * L.heads * qw), 256, 0, st>>>(qf, qt, (size_t)Tn * L.heads * qw);
+                    m->launches++;
+                }
+                // per head: the unrotated query [Tn, dim] times the transposed key expansion [kv_rank, dim]^T
+                GemmIo io = plain_io(L.dim, L.kv_rank);
+                io.lda = L.heads * qw; io.ldy = L.heads * L.kv_rank;
+                io.sa = qw; io.sw = (long long)L.kv_rank * L.dim; io.sy = L.kv_rank;
+                CU(linear_ex<T>(m, qt, static_cast<const T*>(L.w_k_up_t), qlat, Tn, L.kv_rank, L.dim, io, L.heads, 0, st));
+                latent_query_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(P, qf, qlat, qbuf);
                 m->launches += 2;
+                A.G = 1; A.d = dk; A.dv = L.kv_rank;
+                A.k_ld = dk; A.v_ld = dk; A.v_in_k = 1;
+                A.gate_off = (size_t)L.q_rank + dk; A.gate_ld = 1; A.gate_step = 0;
+                A.q_norm = A.k_norm = A.r1 = A.r2 = A.sink = nullptr;
+                if (L.kv_rank <= 256) launch_attention<T, 8>(m, s, A, false, qbuf, pool, mix, st);
+                else launch_attention<T, 16>(m, s, A, false, qbuf, pool, mix, st);
+                // per head: the attended latent [Tn, kv_rank] times the value expansion [vdim, kv_rank]^T
+                GemmIo iv = plain_io(L.kv_rank, L.vdim);
+                iv.lda = L.heads * L.kv_rank; iv.ldy = L.heads * L.vdim;
+                iv.sa = L.kv_rank; iv.sw = (long long)L.vdim * L.kv_rank; iv.sy = L.vdim;
+                CU(linear_ex<T>(m, mix, static_cast<const T*>(L.w_v_up), oraw, Tn, L.vdim, L.kv_rank, iv, L.heads, 0, st));
+                mix_cols = L.heads * L.vdim;
+                if (!kIsF32) {
+                    cast_kernel<T><<<cast_grid((size_t)Tn * mix_cols), 256, 0, st>>>(oraw, mix, (size_t)Tn * mix_cols);
+                    m->launches++;
+                } else {
+                    mix_in = reinterpret_cast<const T*>(oraw);
+                }
             }
-            m->launches += 1;
+        } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
+            GlaArgs A;
+            A.proj = proj; A.n_in = n_in; A.H = L.heads; A.d = L.dim; A.dv = L.vdim; A.rank = L.rank; A.n_tokens = Tn;
+            A.q_scale = L.score_scale; A.tau = L.decay_tau; A.eps = c.norm_eps;
+            A.decay_w2 = L.decay_w2; A.decay_bias = L.decay_bias; A.out_norm = L.out_norm;
+            A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
+            A.slot_floats = m->slot_floats; A.state_off = R.state_off; A.n_slots = m->n_slots; A.err = err;
+            gla_prep_kernel<<<dim3(Tn, (L.heads * L.dim + 127) / 128), 128, L.rank * sizeof(float), st>>>(A, dec);
+            cudaError_t e;
+            if (L.dim <= 16) e = launch_gla_scan<16>(A, s->n_seqs, dec, m->slots, oraw, st);
+            else if (L.dim <= 32) e = launch_gla_scan<32>(A, s->n_seqs, dec, m->slots, oraw, st);
+            else if (L.dim <= 64) e = launch_gla_scan<64>(A, s->n_seqs, dec, m->slots, oraw, st);
+            else if (L.dim <= 128) e = launch_gla_scan<128>(A, s->n_seqs, dec, m->slots, oraw, st);
+            else e = launch_gla_scan<256>(A, s->n_seqs, dec, m->slots, oraw, st);
+            CU(e);
+            gla_out_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(A, oraw, mix);
+            m->launches += 3;
             mix_cols = L.heads * L.vdim;
         } else {
             DeltaArgs A;
@@ -1581,16 +1866,83 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             m->launches += 3;
             mix_cols = L.heads * L.dim;
         }
-        CU(linear<T>(m, mix, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));
+        CU(linear<T>(m, mix_in, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));
         const bool last = n + 1 == m->runs.size();
         const float* next_norm1 = last ? nullptr : m->layers[m->runs[n + 1].layer].norm1;
-        if (L.mlp == SMOL_LM_MLP_POLYNORM) {
+        // the feed-forward reads hn and leaves its output in y
+        auto feed_forward = [&]() -> int {
+            if (L.mlp == SMOL_LM_MLP_POLYNORM) {
+                CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
+                polynorm_kernel<T><<<Tn, 256, 0, st>>>(z, L.act, c.norm_eps, L.ff, act);
+                CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
+                m->launches += 1;
+            } else if (L.mlp == SMOL_LM_MLP_GATED) {
+                CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, 2 * L.ff, D, st));
+                gated_act_kernel<T><<<cast_grid((size_t)Tn * L.ff), 256, 0, st>>>(z, L.ff, L.mlp_act, (size_t)Tn, act);
+                CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
+                m->launches += 1;
+            } else if (L.mlp == SMOL_LM_MLP_EXPERTS) {
+                int32_t* sel_id = reinterpret_cast<int32_t*>(m->ws + m->o_sel_id);
+                float* sel_w = reinterpret_cast<float*>(m->ws + m->o_sel_w);
+                int32_t* perm = reinterpret_cast<int32_t*>(m->ws + m->o_perm);
+                int32_t* slot_of = reinterpret_cast<int32_t*>(m->ws + m->o_slot_of);
+                int32_t* seg = reinterpret_cast<int32_t*>(m->ws + m->o_seg);
+                int32_t* tile_g = reinterpret_cast<int32_t*>(m->ws + m->o_tile_g);
+                int32_t* tile_r = reinterpret_cast<int32_t*>(m->ws + m->o_tile_r);
+                int32_t* n_tiles = reinterpret_cast<int32_t*>(m->ws + m->o_ntiles);
+                float* zp = reinterpret_cast<float*>(m->ws + m->o_zp);
+                T* actp = reinterpret_cast<T*>(m->ws + m->o_actp);
+                float* yp = reinterpret_cast<float*>(m->ws + m->o_yp);
+                RouteArgs Rt;
+                Rt.w_router = L.w_router; Rt.bias = L.route_bias; Rt.D = D; Rt.E = L.n_experts + L.n_identity; Rt.E_real = L.n_experts;
+                Rt.top = L.top_k; Rt.n_groups = L.n_groups; Rt.keep = L.keep_groups; Rt.scale = L.router_scale; Rt.n_tokens = Tn;
+                const int pairs = Tn * L.top_k;
+                // the router reads the sublayer's input in fp32 where the block keeps it (post-norm), else its T form
+                if (postnorm) moe_route_kernel<float><<<Tn, 128, 0, st>>>(Rt, x, sel_id, sel_w);
+                else moe_route_kernel<T><<<Tn, 128, 0, st>>>(Rt, hn, sel_id, sel_w);
+                m->launches += 1;
+                if (L.n_experts > 0) {
+                    moe_index_kernel<<<1, 256, 0, st>>>(sel_id, pairs, L.n_experts, kGroupTile, seg, perm, slot_of, tile_g, tile_r, n_tiles);
+                    const int tiles = pairs / kGroupTile + L.n_experts;
+                    GemmIo io = plain_io(D, 2 * L.ff);
+                    io.sw = (long long)2 * L.ff * D;
+                    io.tile_group = tile_g; io.tile_row0 = tile_r; io.seg = seg; io.n_tiles = n_tiles; io.gather = perm; io.gather_div = L.top_k;
+                    CU(linear_ex<T>(m, hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
+                    gated_act_kernel<T><<<cast_grid((size_t)pairs * L.ff), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
+                    GemmIo io2 = plain_io(L.ff, D);
+                    io2.sw = (long long)D * L.ff;
+                    io2.tile_group = tile_g; io2.tile_row0 = tile_r; io2.seg = seg; io2.n_tiles = n_tiles;
+                    CU(linear_ex<T>(m, actp, static_cast<const T*>(L.w_experts_out), yp, pairs, D, L.ff, io2, 1, tiles, st));
+                    m->launches += 2;
+                } else {
+                    CU(cudaMemsetAsync(slot_of, 0xff, (size_t)pairs * 4, st));
+                }
+                if (postnorm) moe_combine_kernel<float><<<Tn, nthr, 0, st>>>(x, yp, slot_of, sel_w, L.top_k, D, y);
+                else moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, sel_w, L.top_k, D, y);
+                m->launches += 1;
+            }
+            return SMOL_OK;
+        };
+        if (postnorm) {
+            // x <- g1 * rms_divide(alpha x + mixer); x <- g2 * rms_divide(alpha x + ff); the layer's result joins the history
+            // and the stream becomes the weighted sum of the history
+            const bool has_ff = L.mlp != SMOL_LM_MLP_NONE;
+            post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm1, c.norm_eps, D, has_ff ? nullptr : hist,
+                                                                      hist_stride, (int)n + 2, L.depth_mix, nullptr, hn);
+            m->launches += 1;
+            if (has_ff) {
+                const int rc = feed_forward();
+                if (rc != SMOL_OK) return rc;
+                post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm2, c.norm_eps, D, hist, hist_stride,
+                                                                          (int)n + 2, L.depth_mix, nullptr, hn);
+                m->launches += 1;
+            }
+        } else if (L.mlp != SMOL_LM_MLP_NONE) {
             add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn);
-            CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
-            polynorm_kernel<T><<<Tn, 256, 0, st>>>(z, L.act, c.norm_eps, L.ff, act);
-            CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
+            const int rc = feed_forward();
+            if (rc != SMOL_OK) return rc;
             add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn);
-            m->launches += 3;
+            m->launches += 2;
         } else {
             add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn);
             m->launches += 1;
@@ -1598,9 +1950,15 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (s->n_want > 0) {
-        norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
+        if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, D * sizeof(float), st>>>(x, nullptr, 1.0f, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
+                                                                                      nullptr, s->want_rows, hw);
+        else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
         m->launches++;
         CU(linear<T>(m, hw, static_cast<const T*>(m->g.head), s->logits, s->n_want, c.vocab, D, st));
+        if (c.logit_scale != 1.0f) {
+            scale_kernel<<<cast_grid((size_t)s->n_want * c.vocab), 256, 0, st>>>(s->logits, c.logit_scale, (size_t)s->n_want * c.vocab);
+            m->launches++;
+        }
     }
     CU(cudaGetLastError());
     return SMOL_OK;

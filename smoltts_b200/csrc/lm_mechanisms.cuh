@@ -1,0 +1,485 @@
+// Further mechanisms of the hybrid language-model engine (included by lm_kernels.cu after its shared helpers):
+//   - the post-norm block (one gain per norm, the stream scaled before the sublayer's output is added) with the
+//     depth-weighted average of all earlier layer results,
+//   - latent attention (queries through a latent; one cached latent + one rotated shared key part per position),
+//   - the gated linear recurrence (decay per key channel, state [dim, vdim] per head in the sequence's slot),
+//   - gated feed-forwards and the routed mixture of experts (grouped choice, identity outputs).
+// Everything here is fp32 except what is written for a matrix product (T).
+#pragma once
+
+namespace smol {
+namespace lm {
+
+__device__ __forceinline__ float gelu_tanh_(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float silu_(float z) { return z * sigmoidf_(z); }
+__device__ __forceinline__ float gated_act_(int kind, float z) { return kind == SMOL_LM_ACT_SILU ? silu_(z) : gelu_tanh_(z); }
+// ln(sigmoid(z)) without overflow: -(max(-z, 0) + ln(1 + exp(-|z|)))
+__device__ __forceinline__ float log_sigmoid_(float z) { return -(fmaxf(-z, 0.0f) + log1pf(expf(-fabsf(z)))); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Post-norm block.
+// Embedding: X_0 = g * rms_divide(embed[token]); the stream, the first history entry and the first sublayer's input.
+template <class T>
+__global__ void embed_gain_norm_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ embed, int D, int vocab,
+                                       const float* __restrict__ gain, float eps, float* __restrict__ x, float* __restrict__ hist0,
+                                       T* __restrict__ hn) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const T* e = embed + (size_t)tok * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = to_f<T>(e[c]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = gain[0] / sqrtf(ss / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = to_f<T>(e[c]) * r;
+        x[(size_t)t * D + c] = v;
+        hist0[(size_t)t * D + c] = v;
+        hn[(size_t)t * D + c] = from_f<T>(v);
+    }
+}
+
+// x <- g * rms_divide(alpha * x + y).  Inside a layer (hist == nullptr) that is the next sublayer's input.  At the end of
+// a layer the row is the layer's result: it is stored as history entry n_hist - 1, and the stream becomes
+// sum_j mix[j] * history[j] over the n_hist entries (entry 0: the embedding output), summed in ascending j.
+// `rows` selects rows (final norm of the wanted rows): then only hn is written, alpha = 1 and y is not read.
+template <class T>
+__global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ gain, float eps,
+                                 int D, float* __restrict__ hist, size_t hist_stride, int n_hist, const float* __restrict__ mix,
+                                 const int32_t* __restrict__ rows, T* __restrict__ hn) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const size_t o = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * D, oo = (size_t)blockIdx.x * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = rows ? x[o + c] : fmaf(alpha, x[o + c], y[o + c]);
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = gain[0] / sqrtf(ss / (float)D + eps);
+    if (rows) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) hn[oo + c] = from_f<T>(row[c] * r);
+        return;
+    }
+    if (!hist) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            const float v = row[c] * r;
+            x[o + c] = v;
+            hn[o + c] = from_f<T>(v);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = row[c] * r;
+        hist[(size_t)(n_hist - 1) * hist_stride + o + c] = v;
+        float acc = 0.0f;
+        for (int j = 0; j + 1 < n_hist; ++j) acc = fmaf(mix[j], hist[(size_t)j * hist_stride + o + c], acc);
+        acc = fmaf(mix[n_hist - 1], v, acc);
+        x[o + c] = acc;
+        hn[o + c] = from_f<T>(acc);
+    }
+}
+
+// fp32 -> T, n elements (an fp32 matrix-product result that feeds the next product)
+template <class T>
+__global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = from_f<T>(src[i]);
+}
+
+__global__ void scale_kernel(float* __restrict__ v, float scale, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) v[i] *= scale;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Latent attention.  proj row layout: query latent [q_rank] | key/value latent [kv_rank] | shared rotated key [rot] | gate [H].
+// A cached position is ONE row [kv_rank + rot]: the normed latent, then the rotated key part.  Attention runs in the
+// latent space: head h's query is (W_uk[h]^T q_plain[h], rotate(q_rot[h])), its score against a cached row is their dot
+// product, its output the softmax-weighted sum of latents, expanded by W_uv[h] afterwards -- the same numbers as
+// expanding every cached latent into per-head keys and values, without ever doing so.
+struct LatentArgs {
+    const float* proj;
+    int n_in, q_rank, kv_rank, rot, H, d;
+    float eps;
+    const float *q_lat_norm, *kv_lat_norm, *freq;     // freq [rot / 2]: base^(-2i / rot)
+    const int32_t *tok_seq, *tok_pos, *block_table;
+    int max_pages, page_size, n_pages, n_tokens;
+    size_t page_elems, k_off;
+    int32_t* err;
+};
+
+// pair (a, b) of a rotated vector at position pos, pair index i
+__device__ __forceinline__ void rotate_pair(float a, float b, int pos, float freq, float& ra, float& rb) {
+    float sn, cs;
+    sincosf((float)pos * freq, &sn, &cs);
+    ra = a * cs - b * sn;
+    rb = b * cs + a * sn;
+}
+
+// One block per token: the normed query latent -> cq (T), the normed key/value latent and the rotated key part -> the pool.
+template <class T>
+__global__ void latent_prep_kernel(const LatentArgs A, T* __restrict__ cq, T* __restrict__ pool) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const float* row = A.proj + (size_t)t * A.n_in;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) ss += row[c] * row[c];
+    ss = block_sum(ss, red);
+    const float rq = 1.0f / sqrtf(ss / (float)A.q_rank + A.eps);
+    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) cq[(size_t)t * A.q_rank + c] = from_f<T>(row[c] * rq * A.q_lat_norm[c]);
+    const int pos = A.tok_pos[t];
+    const int pg = pos / A.page_size, in_pg = pos % A.page_size;
+    const int page = pg < A.max_pages ? A.block_table[(size_t)A.tok_seq[t] * A.max_pages + pg] : -1;
+    if (page < 0 || page >= A.n_pages) {
+        if (threadIdx.x == 0) atomicExch(A.err, 1);
+        return;
+    }
+    T* dst = pool + (size_t)page * A.page_elems + A.k_off + (size_t)in_pg * (A.kv_rank + A.rot);
+    const float* kv = row + A.q_rank;
+    ss = 0.0f;
+    for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) ss += kv[c] * kv[c];
+    ss = block_sum(ss, red);
+    const float rk = 1.0f / sqrtf(ss / (float)A.kv_rank + A.eps);
+    for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) dst[c] = from_f<T>(kv[c] * rk * A.kv_lat_norm[c]);
+    for (int i = threadIdx.x; i < A.rot / 2; i += blockDim.x) {
+        float ra, rb;
+        rotate_pair(kv[A.kv_rank + 2 * i], kv[A.kv_rank + 2 * i + 1], pos, A.freq[i], ra, rb);
+        dst[A.kv_rank + 2 * i] = from_f<T>(ra);
+        dst[A.kv_rank + 2 * i + 1] = from_f<T>(rb);
+    }
+}
+
+// The attention query of (token, head): qlat (fp32 [T][H][kv_rank], the unrotated query carried into the latent space)
+// followed by the rotated part of q (fp32 [T][H][d + rot]).  One warp per (token, head).
+template <class T>
+__global__ void latent_query_kernel(const LatentArgs A, const float* __restrict__ q, const float* __restrict__ qlat, T* __restrict__ qbuf) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= A.n_tokens * A.H) return;
+    const int t = unit / A.H;
+    const int pos = A.tok_pos[t];
+    T* dst = qbuf + (size_t)unit * (A.kv_rank + A.rot);
+    const float* src = qlat + (size_t)unit * A.kv_rank;
+    for (int c = lane; c < A.kv_rank; c += 32) dst[c] = from_f<T>(src[c]);
+    const float* qr = q + (size_t)unit * (A.d + A.rot) + A.d;
+    for (int i = lane; i < A.rot / 2; i += 32) {
+        float ra, rb;
+        rotate_pair(qr[2 * i], qr[2 * i + 1], pos, A.freq[i], ra, rb);
+        dst[A.kv_rank + 2 * i] = from_f<T>(ra);
+        dst[A.kv_rank + 2 * i + 1] = from_f<T>(rb);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Gated linear recurrence.  proj row layout: q | k [H*d each] | v | gate [H*dv each] | decay-inner [rank].
+//   S_t = diag(w_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t * q_scale,  w = sigmoid(z)^(1/tau), z = W2 inner + bias.
+struct GlaArgs {
+    const float* proj;
+    int n_in, H, d, dv, rank, n_tokens;
+    float q_scale, tau, eps;
+    const float *decay_w2, *decay_bias, *out_norm;     // W2 transposed [rank][H*d] fp32; bias [H*d]; plain norm weight [dv]
+    const int32_t *seq_start, *seq_pos0, *seq_slot;
+    size_t slot_floats, state_off;
+    int n_slots;
+    int32_t* err;
+};
+
+// decay[t][c] for the H*d key channels; blockIdx.y: a slice of blockDim.x channels
+__global__ void gla_prep_kernel(const GlaArgs A, float* __restrict__ decay) {
+    extern __shared__ float inner[];
+    const int t = blockIdx.x, HD = A.H * A.d;
+    const float* row = A.proj + (size_t)t * A.n_in + 2 * HD + 2 * A.H * A.dv;
+    for (int r = threadIdx.x; r < A.rank; r += blockDim.x) inner[r] = row[r];
+    __syncthreads();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= HD) return;
+    float z = A.decay_bias[c];
+#pragma unroll 8
+    for (int r = 0; r < A.rank; ++r) z = fmaf(A.decay_w2[(size_t)r * HD + c], inner[r], z);
+    decay[(size_t)t * HD + c] = expf(log_sigmoid_(z) / A.tau);
+}
+
+// The scan.  Value columns never mix, so a head is cut into groups of CB columns, one block per (sequence, head, group);
+// L adjacent lanes share a column, lane q keeping the key rows 4*(e*L + q) .. +3 of it in registers (DK >= d rows; rows
+// beyond d see zero keys and queries).  q, k, w of the head and v of the block's columns come into shared memory
+// kDeltaChunk tokens at a time by cp.async, the next chunk while the current one is computed.
+__host__ __device__ constexpr int gla_buf_floats(int DK) { return kDeltaChunk * (3 * DK + delta_block_cols(DK)); }
+
+template <int DK, int VEC>
+__device__ __forceinline__ void gla_stage(const GlaArgs& A, float* buf, int c0, int n, int h, int j0, int nc, const float* decay) {
+    constexpr int CB = delta_block_cols(DK), PL = kDeltaChunk * DK;
+    const int d = A.d, HD = A.H * d, dq = d / VEC, ncq = (nc + VEC - 1) / VEC;
+    for (int idx = threadIdx.x; idx < n * dq; idx += blockDim.x) {
+        const int tt = idx / dq, i = (idx - tt * dq) * VEC;
+        const float* prow = A.proj + (size_t)(c0 + tt) * A.n_in + h * d + i;
+        float* dst = buf + tt * DK + i;
+        cp_async_f<VEC>(dst, prow);                                             // q
+        cp_async_f<VEC>(dst + PL, prow + HD);                                   // k
+        cp_async_f<VEC>(dst + 2 * PL, decay + (size_t)(c0 + tt) * HD + h * d + i);
+    }
+    for (int idx = threadIdx.x; idx < n * ncq; idx += blockDim.x) {
+        const int tt = idx / ncq, j = (idx - tt * ncq) * VEC;
+        cp_async_f<VEC>(buf + 3 * PL + tt * CB + j, A.proj + (size_t)(c0 + tt) * A.n_in + 2 * HD + h * A.dv + j0 + j);
+    }
+}
+
+template <int DK>
+__global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_scan_kernel(const GlaArgs A, const float* __restrict__ decay,
+                                                                                         float* __restrict__ state_pool,
+                                                                                         float* __restrict__ o_raw) {
+    constexpr int L = delta_lanes(DK), CB = delta_block_cols(DK), RV = DK / L / 4, PL = kDeltaChunk * DK;
+    constexpr int kBuf = gla_buf_floats(DK);
+    static_assert(DK % (4 * L) == 0, "every lane owns whole 16-byte pieces");
+    extern __shared__ __align__(16) float sh[];
+    const int d = A.d, dv = A.dv, NS = (dv + CB - 1) / CB;
+    const int group = blockIdx.x % NS, sh_id = blockIdx.x / NS;
+    const int seq = sh_id / A.H, h = sh_id % A.H;
+    const int j0 = group * CB;
+    const int nc = min(CB, dv - j0);
+    const int col = threadIdx.x / L, q = threadIdx.x % L, j = j0 + col;
+    const int t0 = A.seq_start[seq], t1 = A.seq_start[seq + 1];
+    const int slot = A.seq_slot[seq];
+    if (slot < 0 || slot >= A.n_slots) {
+        if (threadIdx.x == 0) atomicExch(A.err, 2);
+        return;
+    }
+    // 16-byte copies need every source to start on a 16-byte boundary: d, dv and the row length multiples of 4
+    const bool vec = (d % 4 == 0) && (dv % 4 == 0) && (A.n_in % 4 == 0);
+    for (int i = threadIdx.x; i < 2 * kBuf; i += blockDim.x) sh[i] = 0.0f;      // padded channels and columns stay zero for good
+    __syncthreads();
+    if (vec) gla_stage<DK, 4>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
+    else gla_stage<DK, 1>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
+    cp_async_commit();
+    float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * dv;
+    float S[RV][4];
+    const bool fresh = A.seq_pos0[seq] == 0;
+#pragma unroll
+    for (int e = 0; e < RV; ++e)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = 4 * (e * L + q) + x;
+            S[e][x] = (!fresh && i < d && j < dv) ? st[(size_t)i * dv + j] : 0.0f;
+        }
+    int cur = 0;
+    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk, cur ^= 1) {
+        const int n = min(kDeltaChunk, t1 - c0);
+        cp_async_wait<0>();
+        __syncthreads();                          // this chunk has landed; every thread is done with the other buffer
+        if (c0 + kDeltaChunk < t1) {
+            const int nn = min(kDeltaChunk, t1 - c0 - kDeltaChunk);
+            if (vec) gla_stage<DK, 4>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
+            else gla_stage<DK, 1>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
+            cp_async_commit();
+        }
+        const float* b = sh + cur * kBuf;
+        const float4* s4 = reinterpret_cast<const float4*>(b) + q;      // piece e of a vector of token tt: s4[(tt*DK)/4 + e*L]
+        const float* s_v = b + 3 * PL + col;
+        for (int tt = 0; tt < n; ++tt) {
+            const float v = s_v[tt * CB];
+            float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+            for (int e = 0; e < RV; ++e) {
+                const float4* p = s4 + tt * (DK / 4) + e * L;
+                const float4 qv = p[0], kv = p[PL / 4], wv = p[2 * (PL / 4)];
+                S[e][0] = fmaf(wv.x, S[e][0], kv.x * v);
+                S[e][1] = fmaf(wv.y, S[e][1], kv.y * v);
+                S[e][2] = fmaf(wv.z, S[e][2], kv.z * v);
+                S[e][3] = fmaf(wv.w, S[e][3], kv.w * v);
+                sa = fmaf(S[e][0], qv.x, sa);
+                sb = fmaf(S[e][1], qv.y, sb);
+                sa = fmaf(S[e][2], qv.z, sa);
+                sb = fmaf(S[e][3], qv.w, sb);
+            }
+            float po = sa + sb;
+#pragma unroll
+            for (int s = 1; s < L; s <<= 1) po += __shfl_xor_sync(0xffffffffu, po, s);
+            if (q == 0 && j < dv) o_raw[(size_t)(c0 + tt) * A.H * dv + h * dv + j] = po * A.q_scale;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < RV; ++e)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = 4 * (e * L + q) + x;
+            if (i < d && j < dv) st[(size_t)i * dv + j] = S[e][x];
+        }
+}
+
+// End of the mixer: each head's o divided by its root mean square over dv, times the plain weight [dv] (shared by the
+// heads), times silu(gate), written in T.  One warp per (token, head).
+template <class T>
+__global__ void gla_out_kernel(const GlaArgs A, const float* __restrict__ o_raw, T* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= A.n_tokens * A.H) return;
+    const int t = unit / A.H, h = unit % A.H, dv = A.dv, HV = A.H * dv;
+    const float* o = o_raw + (size_t)t * HV + h * dv;
+    const float* gate = A.proj + (size_t)t * A.n_in + 2 * A.H * A.d + HV + h * dv;
+    float ss = 0.0f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(o[c], o[c], ss);
+    ss = warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)dv + A.eps);
+    for (int c = lane; c < dv; c += 32) out[(size_t)t * HV + h * dv + c] = from_f<T>(o[c] * rs * A.out_norm[c] * silu_(gate[c]));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Gated feed-forward: z rows hold gate [F] | up [F]; out = act(gate) * up in T.
+template <class T>
+__global__ void gated_act_kernel(const float* __restrict__ z, int F, int kind, size_t rows, T* __restrict__ out) {
+    const size_t n = rows * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / F, c = i - r * F;
+        out[i] = from_f<T>(gated_act_(kind, z[r * 2 * F + c]) * z[r * 2 * F + F + c]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Routed mixture of experts.
+struct RouteArgs {
+    const float *w_router, *bias;      // [E][D] fp32, [E]
+    int D, E, E_real, top, n_groups, keep;
+    float scale;
+    int n_tokens;
+};
+constexpr int kMaxRouted = 1024;       // router outputs (experts + identity outputs)
+constexpr int kMaxTop = 32;
+
+// One block per token: fp32 logits over all router outputs, softmax scores s, choice scores s + bias; outputs outside the
+// `keep` best groups (a group's score: its best choice score) cannot be chosen; the `top` best choice scores are chosen
+// (ties: the lower index), their weights are the scores s over their sum, times `scale`.
+template <class TI>
+__global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const TI* __restrict__ x, int32_t* __restrict__ sel_id,
+                                                        float* __restrict__ sel_w) {
+    __shared__ float s[kMaxRouted], choice[kMaxRouted];
+    __shared__ float red[33];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const TI* xr = x + (size_t)t * A.D;
+    for (int e = warp; e < A.E; e += nw) {
+        const float* wr = A.w_router + (size_t)e * A.D;
+        float acc = 0.0f;
+        for (int c = lane; c < A.D; c += 32) acc = fmaf(to_f<TI>(xr[c]), wr[c], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s[e] = acc;
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int e = threadIdx.x; e < A.E; e += blockDim.x) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < nw; ++w) mx = fmaxf(mx, red[w]);
+    float sum = 0.0f;
+    for (int e = threadIdx.x; e < A.E; e += blockDim.x) sum += expf(s[e] - mx);
+    sum = block_sum(sum, red);
+    for (int e = threadIdx.x; e < A.E; e += blockDim.x) {
+        const float p = expf(s[e] - mx) / sum;
+        s[e] = p;
+        choice[e] = p + A.bias[e];
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const int size = A.E / A.n_groups;
+    if (A.keep < A.n_groups) {
+        // drop the n_groups - keep worst groups: repeatedly find the worst group still allowed (ties: the higher index goes)
+        uint32_t dropped[kMaxRouted / 32];
+        for (int i = 0; i < (A.n_groups + 31) / 32; ++i) dropped[i] = 0u;
+        for (int n = 0; n < A.n_groups - A.keep; ++n) {
+            int worst = -1;
+            float ws = 0.0f;
+            for (int g = 0; g < A.n_groups; ++g) {
+                if (dropped[g >> 5] >> (g & 31) & 1u) continue;
+                float gs = -INFINITY;
+                for (int e = g * size; e < (g + 1) * size; ++e) gs = fmaxf(gs, choice[e]);
+                if (worst < 0 || gs <= ws) { worst = g; ws = gs; }
+            }
+            dropped[worst >> 5] |= 1u << (worst & 31);
+            for (int e = worst * size; e < (worst + 1) * size; ++e) choice[e] = -INFINITY;
+        }
+    }
+    int ids[kMaxTop];
+    float den = 0.0f;
+    for (int k = 0; k < A.top; ++k) {
+        int best = -1;
+        float bs = -INFINITY;
+        for (int e = 0; e < A.E; ++e)
+            if (choice[e] > bs) { best = e; bs = choice[e]; }
+        if (best < 0) best = 0;          // fewer allowed outputs than `top`: not a configuration the engine accepts
+        ids[k] = best;
+        choice[best] = -INFINITY;
+        den += s[best];
+    }
+    den += 1e-20f;
+    for (int k = 0; k < A.top; ++k) {
+        sel_id[(size_t)t * A.top + k] = ids[k];
+        sel_w[(size_t)t * A.top + k] = s[ids[k]] / den * A.scale;
+    }
+}
+
+// One block: sorts the (token, choice) pairs of real experts by expert.  seg[e] .. seg[e+1]-1 are expert e's rows in the
+// sorted order, perm[row] the pair of a row, slot_of[pair] its row (-1: an identity output); the tile table cuts every
+// expert's rows into tiles of `tile_rows` for the grouped matrix products.
+__global__ void __launch_bounds__(256) moe_index_kernel(const int32_t* __restrict__ sel_id, int n_pairs, int E_real, int tile_rows,
+                                                        int32_t* __restrict__ seg, int32_t* __restrict__ perm, int32_t* __restrict__ slot_of,
+                                                        int32_t* __restrict__ tile_group, int32_t* __restrict__ tile_row0,
+                                                        int32_t* __restrict__ n_tiles) {
+    __shared__ int count[kMaxRouted + 1], cursor[kMaxRouted];
+    for (int e = threadIdx.x; e <= E_real; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = sel_id[p];
+        if (e < E_real) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E_real; ++e) {
+            const int n = count[e];
+            seg[e] = at;
+            cursor[e] = at;
+            for (int r0 = at; r0 < at + n; r0 += tile_rows) {
+                tile_group[nt] = e;
+                tile_row0[nt] = r0;
+                ++nt;
+            }
+            at += n;
+        }
+        seg[E_real] = at;
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = sel_id[p];
+        int slot = -1;
+        if (e < E_real) {
+            slot = atomicAdd(&cursor[e], 1);
+            perm[slot] = p;
+        }
+        slot_of[p] = slot;
+    }
+}
+
+// y[t] = sum_k w[t][k] * (expert output of pair (t, k), or the input x[t] for an identity output), k ascending.
+template <class TI>
+__global__ void moe_combine_kernel(const TI* __restrict__ x, const float* __restrict__ yp, const int32_t* __restrict__ slot_of,
+                                   const float* __restrict__ sel_w, int top, int D, float* __restrict__ y) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = slot_of[(size_t)t * top + k];
+            const float v = slot >= 0 ? yp[(size_t)slot * D + c] : to_f<TI>(x[(size_t)t * D + c]);
+            acc = fmaf(sel_w[(size_t)t * top + k], v, acc);
+        }
+        y[(size_t)t * D + c] = acc;
+    }
+}
+
+}  // namespace lm
+}  // namespace smol

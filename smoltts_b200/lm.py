@@ -1,8 +1,12 @@
 """Host side of the hybrid language-model engine: checkpoint loading, pools, and the ragged-batch step.
 
+``HybridLM`` is the engine of every design; a design's class says how its checkpoint maps onto the engine's layers.
 ``PamasunLM`` serves the Pamasun design: a decoder-only model whose layers mix tokens either by causal attention with a
 softmax sink (keys and values in a paged pool) or by a generalized delta rule (a matrix state per head, kept in a
 per-sequence slot), with PolyNorm feed-forwards, pre- and post-norms around every sublayer and layer scales.
+``MaferaxLM`` serves the Maferax design: post-norm layers with one gain per norm and a depth-weighted average of all
+earlier layer results; latent attention (one cached latent and one rotated shared key part per position, in the paged
+pool) or a gated linear recurrence (state per head in the slot); gated feed-forwards or a routed mixture of experts.
 
 The engine owns two pools -- key/value pages (``PagePool``) and state slots (``SlotPool``) -- and one step function,
 ``forward``: any number of sequences, each with its next tokens (a portion of a prompt or a single decoded token).
@@ -23,7 +27,8 @@ import torch
 
 from . import _capi_lm
 from ._errors import SMOL_ERR_CAPACITY, SmolError
-from .lm_config import MIXER_KINDS, MLP_KINDS, PamasunConfig
+from .lm_config import (ACT_GELU_TANH, ACT_SILU, BLOCK_POSTNORM, BLOCK_SANDWICH, MAFERAX_MLP_KINDS, MIXER_KINDS, MLP_KINDS,
+                        MaferaxConfig, PamasunConfig)
 from .pool import PagePool, SlotPool
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "I32": torch.int32, "I64": torch.int64}
@@ -41,7 +46,7 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
             continue
         lo, hi = meta["data_offsets"]
         t = torch.frombuffer(bytearray(data[lo:hi]), dtype=_ST_DTYPES[meta["dtype"]]) if hi > lo else torch.empty(0, dtype=_ST_DTYPES[meta["dtype"]])
-        out[name] = t.view(*meta["shape"])
+        out[name] = t.reshape(meta["shape"])          # () for a single number
     return out
 
 
@@ -57,12 +62,14 @@ class Sequence_:
         self.length = 0
 
 
-class PamasunLM:
-    """B200 engine of one Pamasun checkpoint."""
+class HybridLM:
+    """B200 engine of one hybrid language-model checkpoint.  Subclasses name the design's configuration class and map
+    its checkpoint onto the engine's layer structs (``_describe``)."""
 
-    architecture = "Pamasun"
+    architecture = ""
+    config_class = None
 
-    def __init__(self, config: PamasunConfig, dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None,
+    def __init__(self, config, dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None,
                  max_tokens: int = 8192, max_seqs: int = 4, page_size: int = 64, max_step_tokens: int = 2048,
                  max_want: Optional[int] = None, use_graph: bool = True):
         if not torch.cuda.is_available():
@@ -90,19 +97,28 @@ class PamasunLM:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def from_pretrained(cls, path: str, dtype: torch.dtype = torch.bfloat16, **engine_kwargs) -> "PamasunLM":
-        config = PamasunConfig.from_pretrained(str(path))
+    def from_pretrained(cls, path: str, dtype: torch.dtype = torch.bfloat16, **engine_kwargs):
+        config = cls.config_class.from_pretrained(str(path))
         model = cls(config, dtype=dtype, **engine_kwargs)
         model.load_state_dict(read_safetensors(str(Path(path) / "model.safetensors")))
         return model
+
+    # -- what a design's class provides --
+    def _shapes(self, sd: Dict[str, torch.Tensor]) -> Dict[str, tuple]:
+        """Tensor names and shapes the checkpoint must hold (sizes the configuration leaves open are read from ``sd``)."""
+        raise NotImplementedError
+
+    def _describe(self, sd, layers, mat, vec) -> Dict[str, object]:
+        """Fills the engine's layer structs from the checkpoint; ``mat(*names)`` uploads matrices (stacked along the output
+        axis) in the engine's element type, ``vec(name)`` a vector or single number in fp32; both return device tensors that
+        the engine keeps alive.  Returns {"config": extra SmolLmConfig fields, "globals": SmolLmGlobals fields as tensors}."""
+        raise NotImplementedError
 
     def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
         """Binds a checkpoint: matrices in the engine's element type (per-mixer input projections fused into one matrix),
         vectors in fp32; creates the engine for the sizes found and carves its pools."""
         cfg, dev, dt = self.config, self.device, self.dtype
-        rank_of = {i: int(sd[f"l{i}.mix.w1"].shape[0]) for i, L in enumerate(cfg.layers)
-                   if L.mixer.kind == "general_delta" and f"l{i}.mix.w1" in sd}
-        want = cfg.tensor_shapes(rank_of)
+        want = self._shapes(sd)
         missing = [k for k in want if k not in sd]
         if missing:
             raise KeyError(f"checkpoint is missing {missing[:4]}{'...' if len(missing) > 4 else ''}")
@@ -111,55 +127,34 @@ class PamasunLM:
                 raise ValueError(f"shape mismatch for {k}: {tuple(sd[k].shape)} vs {tuple(shape)}")
         self.weights = {k: sd[k] for k in want}
 
-        def mat(*names: str) -> torch.Tensor:
-            t = torch.cat([sd[n].to(torch.float32) for n in names], 0).to(device=dev, dtype=dt).contiguous()
+        def keep(t: torch.Tensor) -> torch.Tensor:
             self._keep.append(t)
             return t
 
-        def vec(name: str) -> torch.Tensor:
-            t = sd[name].to(device=dev, dtype=torch.float32).contiguous()
-            self._keep.append(t)
-            return t
+        def mat(*names: str) -> torch.Tensor:
+            return keep(torch.cat([(sd[n] if isinstance(n, str) else n).to(torch.float32) for n in names], 0).to(device=dev, dtype=dt).contiguous())
+
+        def vec(name) -> torch.Tensor:
+            return keep((sd[name] if isinstance(name, str) else name).to(device=dev, dtype=torch.float32).reshape(-1).contiguous())
 
         self._keep = []
         layers = (_capi_lm.SmolLmLayer * len(cfg.layers))()
-        for i, L in enumerate(cfg.layers):
-            p, m, c = f"l{i}.", L.mixer, layers[i]
-            c.mixer, c.heads, c.kv_heads, c.dim, c.vdim = MIXER_KINDS[m.kind], m.heads, m.kv_heads, m.dim, m.vdim
-            c.mlp, c.ff = MLP_KINDS[L.mlp_kind], L.ff
-            c.score_scale, c.decay_coef, c.unit_eps = m.scale, m.decay_coef, m.unit_eps
-            for nm in ("norm1", "norm1b", "ls1"):
-                setattr(c, nm, vec(p + nm).data_ptr())
-            if m.kind == "attention":
-                c.rank = 0
-                c.w_in = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g").data_ptr()
-                c.q_norm, c.k_norm = vec(p + "mix.q.norm").data_ptr(), vec(p + "mix.k.norm").data_ptr()
-                c.dist_r1, c.dist_r2, c.sink = vec(p + "mix.r1").data_ptr(), vec(p + "mix.r2").data_ptr(), vec(p + "mix.sink").data_ptr()
-            else:
-                c.rank = rank_of[i]
-                c.w_in = mat(p + "mix.r", p + "mix.k", p + "mix.v", p + "mix.g", p + "mix.a", p + "mix.w1").data_ptr()
-                w2t = sd[p + "mix.w2"].to(device=dev, dtype=torch.float32).t().contiguous()      # [rank, heads * dim]: coalesced per channel
-                self._keep.append(w2t)
-                c.rate_bias, c.decay_w2 = vec(p + "mix.a.b").data_ptr(), w2t.data_ptr()
-                c.decay_bias, c.out_norm = vec(p + "mix.w0").data_ptr(), vec(p + "mix.norm").data_ptr()
-            c.w_out = mat(p + "mix.o").data_ptr()
-            if L.mlp_kind:
-                c.w_up, c.w_down = mat(p + "mlp.up").data_ptr(), mat(p + "mlp.down").data_ptr()
-                for nm in ("norm2", "norm2b", "ls2"):
-                    setattr(c, nm, vec(p + nm).data_ptr())
-                c.act = vec(p + "mlp.act").data_ptr()
+        desc = self._describe(sd, layers, mat, vec)
         ccfg = _capi_lm.SmolLmConfig(
             dtype=_capi_lm.SMOL_LM_F32 if dt == torch.float32 else _capi_lm.SMOL_LM_BF16, vocab=cfg.vocab, width=cfg.width,
             n_layers=len(cfg.layers), n_runs=len(self.runs), page_size=self.page_size, max_step_tokens=self.max_step_tokens,
             max_step_seqs=self.max_seqs, max_want=self.max_want,
-            max_context=self.page_pool.n * self.page_size, use_graph=int(self.use_graph), embed_scale=cfg.embedding_scale, norm_eps=cfg.norm_eps)
+            max_context=self.page_pool.n * self.page_size, use_graph=int(self.use_graph), embed_scale=1.0, norm_eps=cfg.norm_eps,
+            block=BLOCK_SANDWICH, residual_alpha=1.0, logit_scale=1.0)
+        for k, v in desc["config"].items():
+            setattr(ccfg, k, v)
         runs = (C.c_int32 * len(self.runs))(*self.runs)
         if self._h:
             self.lib.smol_lm_destroy(self._h)
         h = C.c_void_p()
         _capi_lm.check(self.lib.smol_lm_create(C.byref(ccfg), layers, runs, C.byref(h)))
         self._h = h
-        g = _capi_lm.SmolLmGlobals(embed=mat("embed").data_ptr(), head=mat("head").data_ptr(), final_norm=vec("final.norm").data_ptr())
+        g = _capi_lm.SmolLmGlobals(**{k: v.data_ptr() for k, v in desc["globals"].items()})
         with torch.cuda.device(dev):
             self.page_bytes = self.lib.smol_lm_page_bytes(h)
             self.slot_bytes = self.lib.smol_lm_slot_bytes(h)
@@ -319,3 +314,101 @@ class PamasunLM:
     @property
     def launch_count(self) -> int:
         return int(self.lib.smol_lm_launch_count(self._h))
+
+
+class PamasunLM(HybridLM):
+    """B200 engine of one Pamasun checkpoint."""
+
+    architecture = "Pamasun"
+    config_class = PamasunConfig
+
+    def _rank_of(self, sd) -> Dict[int, int]:
+        return {i: int(sd[f"l{i}.mix.w1"].shape[0]) for i, L in enumerate(self.config.layers)
+                if L.mixer.kind == "general_delta" and f"l{i}.mix.w1" in sd}
+
+    def _shapes(self, sd):
+        return self.config.tensor_shapes(self._rank_of(sd))
+
+    def _describe(self, sd, layers, mat, vec):
+        cfg, rank_of = self.config, self._rank_of(sd)
+        for i, L in enumerate(cfg.layers):
+            p, m, c = f"l{i}.", L.mixer, layers[i]
+            c.mixer, c.heads, c.kv_heads, c.dim, c.vdim = MIXER_KINDS[m.kind], m.heads, m.kv_heads, m.dim, m.vdim
+            c.mlp, c.ff = MLP_KINDS[L.mlp_kind], L.ff
+            c.score_scale, c.decay_coef, c.unit_eps = m.scale, m.decay_coef, m.unit_eps
+            for nm in ("norm1", "norm1b", "ls1"):
+                setattr(c, nm, vec(p + nm).data_ptr())
+            if m.kind == "attention":
+                c.rank = 0
+                c.w_in = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g").data_ptr()
+                c.q_norm, c.k_norm = vec(p + "mix.q.norm").data_ptr(), vec(p + "mix.k.norm").data_ptr()
+                c.dist_r1, c.dist_r2, c.sink = vec(p + "mix.r1").data_ptr(), vec(p + "mix.r2").data_ptr(), vec(p + "mix.sink").data_ptr()
+            else:
+                c.rank = rank_of[i]
+                c.w_in = mat(p + "mix.r", p + "mix.k", p + "mix.v", p + "mix.g", p + "mix.a", p + "mix.w1").data_ptr()
+                c.rate_bias = vec(p + "mix.a.b").data_ptr()
+                c.decay_w2 = vec(sd[p + "mix.w2"].to(torch.float32).t().contiguous()).data_ptr()      # [rank, heads * dim]: coalesced per channel
+                c.decay_bias, c.out_norm = vec(p + "mix.w0").data_ptr(), vec(p + "mix.norm").data_ptr()
+            c.w_out = mat(p + "mix.o").data_ptr()
+            if L.mlp_kind:
+                c.w_up, c.w_down = mat(p + "mlp.up").data_ptr(), mat(p + "mlp.down").data_ptr()
+                for nm in ("norm2", "norm2b", "ls2"):
+                    setattr(c, nm, vec(p + nm).data_ptr())
+                c.act = vec(p + "mlp.act").data_ptr()
+        return {"config": {"embed_scale": cfg.embedding_scale},
+                "globals": {"embed": mat("embed"), "head": mat("head"), "final_norm": vec("final.norm")}}
+
+
+class MaferaxLM(HybridLM):
+    """B200 engine of one Maferax checkpoint."""
+
+    architecture = "Maferax"
+    config_class = MaferaxConfig
+
+    def _rank_of(self, sd) -> Dict[int, int]:
+        return {i: int(sd[f"l{i}.mix.a1"].shape[0]) for i, L in enumerate(self.config.layers)
+                if L.mixer.kind == "gla" and f"l{i}.mix.a1" in sd}
+
+    def _shapes(self, sd):
+        return self.config.tensor_shapes(self._rank_of(sd))
+
+    def _describe(self, sd, layers, mat, vec):
+        cfg, rank_of = self.config, self._rank_of(sd)
+        for i, L in enumerate(cfg.layers):
+            p, m, c = f"l{i}.", L.mixer, layers[i]
+            c.mixer, c.heads, c.dim, c.vdim = MIXER_KINDS[m.kind], m.heads, m.dim, m.vdim
+            c.norm1 = vec(p + "norm1").data_ptr()
+            c.depth_mix = vec(p + "dwa").data_ptr()
+            if m.kind == "latent_attention":
+                c.kv_heads, c.rank = 1, 0
+                c.rot_dim, c.q_rank, c.kv_rank, c.rot_base, c.score_scale = m.rot_dim, m.q_rank, m.kv_rank, m.rot_base, m.scale
+                c.w_in = mat(p + "mix.dq", p + "mix.dkv", p + "mix.g").data_ptr()
+                c.w_q_up = mat(p + "mix.uq").data_ptr()
+                # the key expansion of every head, transposed: [heads][kv_rank][dim] (exact: a change of layout only)
+                uk = sd[p + "mix.uk"].to(torch.float32).view(m.heads, m.dim, m.kv_rank).transpose(1, 2).reshape(m.heads * m.kv_rank, m.dim)
+                c.w_k_up_t = mat(uk).data_ptr()
+                c.w_v_up = mat(p + "mix.uv").data_ptr()
+                c.q_lat_norm, c.kv_lat_norm = vec(p + "mix.dq.norm").data_ptr(), vec(p + "mix.dkv.norm").data_ptr()
+            else:
+                c.kv_heads, c.rank = m.heads, rank_of[i]
+                c.score_scale, c.decay_tau = m.dim ** -0.5, m.tau
+                c.w_in = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g", p + "mix.a1").data_ptr()
+                c.decay_w2 = vec(sd[p + "mix.a2"].to(torch.float32).t().contiguous()).data_ptr()      # [rank, heads * dim]
+                c.decay_bias, c.out_norm = vec(p + "mix.a2.b").data_ptr(), vec(p + "mix.norm").data_ptr()
+            c.w_out = mat(p + "mix.o").data_ptr()
+            c.mlp, c.ff = MAFERAX_MLP_KINDS[L.mlp_kind], L.ff
+            if L.mlp_kind:
+                c.norm2 = vec(p + "norm2").data_ptr()
+            if L.mlp_kind == "dense":
+                c.mlp_act = ACT_GELU_TANH
+                c.w_up, c.w_down = mat(p + "mlp.gate", p + "mlp.up").data_ptr(), mat(p + "mlp.down").data_ptr()
+            elif L.mlp_kind == "moe":
+                r = L.router
+                c.mlp_act = ACT_SILU
+                c.n_experts, c.n_identity, c.top_k, c.n_groups, c.keep_groups, c.router_scale = r.experts, r.identity, r.top, r.groups, r.keep, r.scale
+                if r.experts:
+                    c.w_experts_in = mat(*[f"{p}mlp.e{e}.{nm}" for e in range(r.experts) for nm in ("gate", "up")]).data_ptr()
+                    c.w_experts_out = mat(*[f"{p}mlp.e{e}.down" for e in range(r.experts)]).data_ptr()
+                c.w_router, c.route_bias = vec(p + "mlp.router").data_ptr(), vec(p + "mlp.correction").data_ptr()
+        return {"config": {"block": BLOCK_POSTNORM, "residual_alpha": cfg.postln_alpha, "logit_scale": cfg.logit_scale},
+                "globals": {"embed": mat("embed"), "head": mat("head"), "final_norm": vec("final.norm"), "embed_norm": vec("embed.norm")}}

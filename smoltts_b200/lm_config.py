@@ -13,8 +13,13 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Dict, List, Optional
 
-MIXER_KINDS = {"attention": 0, "general_delta": 1}      # values of SMOL_LM_MIX_* (include/smoltts_b200_lm.h)
-MLP_KINDS = {None: 0, "dense": 1}                        # SMOL_LM_MLP_*: "dense" = up, PolyNorm, down
+# values of SMOL_LM_MIX_* (include/smoltts_b200_lm.h)
+MIXER_KINDS = {"attention": 0, "general_delta": 1, "latent_attention": 2, "gla": 3}
+MLP_KINDS = {None: 0, "dense": 1}                        # SMOL_LM_MLP_* of Pamasun: "dense" = up, PolyNorm, down
+# SMOL_LM_MLP_* of Maferax: "dense" = gated (tanh-form gelu), "moe" = routed mixture of gated (silu) experts
+MAFERAX_MLP_KINDS = {None: 0, "dense": 2, "moe": 3}
+ACT_GELU_TANH, ACT_SILU = 0, 1                           # SMOL_LM_ACT_*
+BLOCK_SANDWICH, BLOCK_POSTNORM = 0, 1                    # SMOL_LM_BLOCK_*
 
 
 @dataclass
@@ -31,8 +36,8 @@ class MixerSpec:
 
     @classmethod
     def from_dict(cls, kind: str, d: Dict[str, Any]) -> "MixerSpec":
-        if kind not in MIXER_KINDS:
-            raise ValueError(f"unknown mixer type {kind!r}; have {sorted(MIXER_KINDS)}")
+        if kind not in ("attention", "general_delta"):
+            raise ValueError(f"unknown mixer type {kind!r}; have ['attention', 'general_delta']")
         if kind == "attention":
             # kv_heads and vdim default to heads and dim (plain multi-head attention with square heads)
             return cls(kind, int(d["heads"]), int(d["dim"]), int(d.get("kv_heads", d["heads"])), int(d.get("vdim", d["dim"])), float(d["scale"]))
@@ -155,3 +160,193 @@ class PamasunConfig:
             if len(s) == 2 and k.startswith("l"):
                 per_layer[int(k[1:k.index(".")])] += 2 * s[0] * s[1]
         return sum(per_layer[i] for i in self.layer_runs()) + 2 * self.vocab * self.width
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Maferax: post-norm layers (one gain per norm) with a depth-weighted average of all earlier layer results; mixers are
+# latent attention (low-rank queries and keys/values, a rotated shared key part) and a gated linear recurrence;
+# feed-forwards are gated (dense) or a routed mixture of experts with grouped choice and identity outputs.
+
+
+@dataclass
+class LatentAttentionSpec:
+    kind = "latent_attention"
+    heads: int
+    dim: int              # unrotated query/key coordinates per head
+    rot_dim: int          # rotated coordinates per head (after the unrotated ones); the rotated key part is shared by the heads
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot_base: float
+    rot_dims: int         # coordinates the rotation acts on (here: all rot_dim)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "LatentAttentionSpec":
+        rot = d["rot"]
+        spec = cls(int(d["heads"]), int(d["dim"]), int(d["rot_dim"]), int(d["vdim"]), int(d["q_rank"]), int(d["kv_rank"]),
+                   float(d["scale"]), float(rot["base"]), int(rot.get("dims", d["rot_dim"])))
+        if spec.rot_dims != spec.rot_dim or spec.rot_dim % 2:
+            raise ValueError("latent attention rotates its whole rotated part: rot.dims must equal rot_dim, and be even")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim, "q_rank": self.q_rank,
+                "kv_rank": self.kv_rank, "scale": self.scale, "rot": {"base": self.rot_base, "dims": self.rot_dims}}
+
+
+@dataclass
+class GatedLinearSpec:
+    kind = "gla"
+    heads: int
+    dim: int              # key channels per head
+    vdim: int
+    tau: float            # decay = sigmoid(z)^(1/tau)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "GatedLinearSpec":
+        return cls(int(d["heads"]), int(d["dim"]), int(d["vdim"]), float(d["tau"]))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "tau": self.tau}
+
+
+@dataclass
+class RouterSpec:
+    experts: int
+    identity: int
+    top: int
+    groups: int
+    keep: int
+    scale: float
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "RouterSpec":
+        g = d.get("groups") or {"count": 1, "keep": 1}
+        spec = cls(int(d["experts"]), int(d.get("identity", 0)), int(d["top"]), int(g["count"]), int(g["keep"]), float(d.get("scale", 1.0)))
+        total = spec.experts + spec.identity
+        if total % spec.groups or not 1 <= spec.keep <= spec.groups or spec.top > spec.keep * (total // spec.groups):
+            raise ValueError(f"router: {total} outputs do not form {spec.groups} equal groups of which {spec.keep} can hold {spec.top} choices")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"experts": self.experts, "identity": self.identity, "top": self.top, "groups": {"count": self.groups, "keep": self.keep},
+                "scale": self.scale}
+
+
+@dataclass
+class MaferaxLayer:
+    mixer: Any                               # LatentAttentionSpec | GatedLinearSpec
+    mlp_kind: Optional[str] = None           # None | "dense" | "moe"
+    ff: int = 0                              # dense: feed-forward size; moe: size of one expert
+    router: Optional[RouterSpec] = None
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "MaferaxLayer":
+        kinds = {"latent_attention": LatentAttentionSpec, "gla": GatedLinearSpec}
+        if d["type"] not in kinds:
+            raise ValueError(f"unknown mixer type {d['type']!r}; have {sorted(kinds)}")
+        mixer = kinds[d["type"]].from_dict(d["mixer"])
+        mlp = d.get("mlp")
+        if not mlp:
+            return cls(mixer)
+        if mlp["kind"] == "dense":
+            return cls(mixer, "dense", int(mlp["ff"]))
+        if mlp["kind"] == "moe":
+            return cls(mixer, "moe", int(mlp["expert"]["ff"]), RouterSpec.from_dict(mlp["router"]))
+        raise ValueError(f"unknown feed-forward kind {mlp['kind']!r}")
+
+    def to_dict(self) -> Dict[str, Any]:
+        mlp = None
+        if self.mlp_kind == "dense":
+            mlp = {"kind": "dense", "ff": self.ff}
+        elif self.mlp_kind == "moe":
+            mlp = {"kind": "moe", "expert": {"ff": self.ff}, "router": self.router.to_dict()}
+        return {"type": self.mixer.kind, "mixer": self.mixer.to_dict(), "mlp": mlp}
+
+
+@dataclass
+class MaferaxConfig:
+    architecture: str = "Maferax"
+    vocab: int = 0
+    width: int = 0
+    norm_eps: float = 1e-6
+    postln_alpha: float = 1.0
+    logit_scale: float = 1.0
+    layers: List[MaferaxLayer] = field(default_factory=list)
+    extra: Dict[str, Any] = field(default_factory=dict, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "MaferaxConfig":
+        known = {"architecture", "vocab", "width", "norm", "postln_alpha", "logit_scale", "layers"}
+        return cls(architecture=d.get("architecture", "Maferax"), vocab=int(d["vocab"]), width=int(d["width"]),
+                   norm_eps=float(d["norm"]["eps"]), postln_alpha=float(d["postln_alpha"]), logit_scale=float(d.get("logit_scale", 1.0)),
+                   layers=[MaferaxLayer.from_dict(x) for x in d["layers"]], extra={k: v for k, v in d.items() if k not in known})
+
+    @classmethod
+    def from_pretrained(cls, pathname: str) -> "MaferaxConfig":
+        path = Path(pathname)
+        if path.is_dir():
+            path = path / "config.json"
+        with open(path, "r", encoding="utf-8") as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = dict(self.extra)
+        d.update(architecture=self.architecture, vocab=self.vocab, width=self.width, norm={"eps": self.norm_eps},
+                 postln_alpha=self.postln_alpha, logit_scale=self.logit_scale, layers=[x.to_dict() for x in self.layers])
+        return d
+
+    def save(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.to_dict(), f, indent=1, sort_keys=True)
+
+    def layer_runs(self) -> List[int]:
+        return list(range(len(self.layers)))
+
+    def tensor_shapes(self, rank_of: Optional[Dict[int, int]] = None) -> Dict[str, tuple]:
+        """Checkpoint tensor names and shapes.  The inner size of the recurrence's decay projection is not in the
+        configuration: it is read from the checkpoint (``rank_of[layer]``), 16 where unknown."""
+        D, V = self.width, self.vocab
+        out: Dict[str, tuple] = {"embed": (V, D), "embed.norm": (), "head": (V, D), "final.norm": ()}
+        for i, L in enumerate(self.layers):
+            p, m = f"l{i}.", L.mixer
+            out[p + "norm1"] = ()
+            out[p + "dwa"] = (i + 2,)
+            if m.kind == "latent_attention":
+                out.update({p + "mix.dq": (m.q_rank, D), p + "mix.dq.norm": (m.q_rank,), p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank),
+                            p + "mix.dkv": (m.kv_rank + m.rot_dim, D), p + "mix.dkv.norm": (m.kv_rank,),
+                            p + "mix.uk": (m.heads * m.dim, m.kv_rank), p + "mix.uv": (m.heads * m.vdim, m.kv_rank),
+                            p + "mix.g": (m.heads, D), p + "mix.o": (D, m.heads * m.vdim)})
+            else:
+                hd, hv, rank = m.heads * m.dim, m.heads * m.vdim, (rank_of or {}).get(i, 16)
+                out.update({p + "mix.q": (hd, D), p + "mix.k": (hd, D), p + "mix.v": (hv, D), p + "mix.g": (hv, D), p + "mix.o": (D, hv),
+                            p + "mix.norm": (m.vdim,), p + "mix.a1": (rank, D), p + "mix.a2": (hd, rank), p + "mix.a2.b": (hd,)})
+            if L.mlp_kind:
+                out[p + "norm2"] = ()
+            if L.mlp_kind == "dense":
+                out.update({p + "mlp.gate": (L.ff, D), p + "mlp.up": (L.ff, D), p + "mlp.down": (D, L.ff)})
+            elif L.mlp_kind == "moe":
+                total = L.router.experts + L.router.identity
+                for e in range(L.router.experts):
+                    out.update({f"{p}mlp.e{e}.gate": (L.ff, D), f"{p}mlp.e{e}.up": (L.ff, D), f"{p}mlp.e{e}.down": (D, L.ff)})
+                out.update({p + "mlp.router": (total, D), p + "mlp.correction": (total,)})
+        return out
+
+    # ---- accounting used by the benchmark ----
+    def weight_elements(self, rank: int = 16, active_only: bool = False) -> int:
+        """Matrix elements of the model without the embedding table; ``active_only``: those one token touches (``top`` experts)."""
+        shapes = self.tensor_shapes({i: rank for i in range(len(self.layers))})
+        total = 0
+        for k, s in shapes.items():
+            if len(s) != 2 or k == "embed":
+                continue
+            n = s[0] * s[1]
+            if active_only and ".mlp.e" in k:
+                L = self.layers[int(k[1:k.index(".")])]
+                n = n * L.router.top / max(L.router.experts, 1)
+            total += n
+        return int(total)
+
+    def matmul_flops_per_token(self, rank: int = 16) -> int:
+        return 2 * self.weight_elements(rank, active_only=True)

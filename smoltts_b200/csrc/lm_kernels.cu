@@ -903,13 +903,16 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int cols, RowPtr src) {
 
 // The exponentials and the penalty's logarithm use the hardware approximations (relative error about 2^-22): this form
 // serves bf16 only, whose products carry 2^-9.
-template <int DP>
+// DK / DV: key and value sizes padded to multiples of 16.  VK: the values are the first columns of the key rows (a cached
+// latent that serves as both), so only key tiles are staged and DV <= DK.
+template <int DK, int DV, bool VK>
 __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const bf16* __restrict__ qbuf, const bf16* __restrict__ pool,
                                                          bf16* __restrict__ out) {
-    constexpr int LD = DP + 8, kTile = 64 * LD;
-    extern __shared__ __align__(16) unsigned char flash_smem[];      // keys [2][64][LD], values [2][64][LD]: two tiles in turn
+    constexpr int LD = DK + 8, kTile = 64 * LD, LDV = VK ? LD : DV + 8, kTileV = 64 * LDV;
+    static_assert(!VK || DV <= DK, "values inside the key rows");
+    extern __shared__ __align__(16) unsigned char flash_smem[];      // keys [2][64][LD], values [2][64][LDV]: two tiles in turn
     bf16* Ks = reinterpret_cast<bf16*>(flash_smem);
-    bf16* Vs = Ks + 2 * kTile;
+    bf16* Vs = VK ? Ks : Ks + 2 * kTile;
     const int s = blockIdx.y;
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
     const int tile = gridDim.x - 1 - blockIdx.x;      // the tiles with the most keys start first
@@ -919,13 +922,13 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     const int pos0 = A.tok_pos[t0];
     const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
     // queries of the tile -> A fragments
-    stage_rows<DP, false>(Ks, A.d, [&](int row) -> const bf16* {
+    stage_rows<DK, false>(Ks, A.d, [&](int row) -> const bf16* {
         return tile * 64 + row < n ? qbuf + ((size_t)(t0 + tile * 64 + row) * A.H + h) * A.d : nullptr;
     });
     __syncthreads();
-    uint32_t qf[DP / 16][4];
+    uint32_t qf[DK / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < DP / 16; ++kk) {
+    for (int kk = 0; kk < DK / 16; ++kk) {
         const bf16* p = Ks + (warp * 16 + gq) * LD + kk * 16 + tq * 2;
         qf[kk][0] = *reinterpret_cast<const uint32_t*>(p);
         qf[kk][1] = *reinterpret_cast<const uint32_t*>(p + 8 * LD);
@@ -936,11 +939,12 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     const int row_a = tile * 64 + warp * 16 + gq, row_b = row_a + 8;
     const int i_a = pos0 + row_a, i_b = pos0 + row_b;
     const int last_pos = pos0 + min(n, tile * 64 + 64) - 1;
-    const float r1 = A.r1[h], r2 = A.r2[h], sink = A.sink[h];
-    float m_a = sink, m_b = sink, l_a = tq == 0 ? 1.0f : 0.0f, l_b = l_a;
-    float o[DP / 8][4];
+    const bool penalty = A.r1 != nullptr;
+    const float r1 = penalty ? A.r1[h] : 0.0f, r2 = penalty ? A.r2[h] : 0.0f, sink = A.sink ? A.sink[h] : -INFINITY;
+    float m_a = sink, m_b = sink, l_a = (tq == 0 && A.sink) ? 1.0f : 0.0f, l_b = l_a;
+    float o[DV / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < DP / 8; ++nt)
+    for (int nt = 0; nt < DV / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[nt][e] = 0.0f;
     // the next tile of keys and values is on its way (cp.async) while the current one is multiplied
@@ -950,8 +954,8 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             if (j > last_pos) return nullptr;
             return pool + (size_t)bt[j / A.page_size] * A.page_elems + off + ((size_t)g * A.page_size + j % A.page_size) * width;
         };
-        stage_rows<DP, true>(Ks + buf * kTile, A.d, [&](int row) { return row_of(row, A.k_off, A.d); });
-        stage_rows<DP, true>(Vs + buf * kTile, A.dv, [&](int row) { return row_of(row, A.v_off, A.dv); });
+        stage_rows<DK, true>(Ks + buf * kTile, A.d, [&](int row) { return row_of(row, A.k_off, A.k_ld); });
+        if (!VK) stage_rows<DV, true>(Vs + buf * kTileV, A.dv, [&](int row) { return row_of(row, A.v_off, A.v_ld); });
         cp_async_commit_group();
     };
     stage_tile(0, 0);
@@ -965,7 +969,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
         }
         __syncthreads();
         const bf16* Kt = Ks + buf * kTile;
-        const bf16* Vt = Vs + buf * kTile;
+        const bf16* Vt = Vs + buf * kTileV;
         if (j0 <= pos0 + tile * 64 + warp * 16 + 15) {          // this warp's rows see at least one key of the tile
             float S[8][4];
 #pragma unroll
@@ -973,7 +977,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
 #pragma unroll
                 for (int e = 0; e < 4; ++e) S[nt][e] = 0.0f;
 #pragma unroll
-            for (int kk = 0; kk < DP / 16; ++kk)
+            for (int kk = 0; kk < DK / 16; ++kk)
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
                     const bf16* p = Kt + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
@@ -987,7 +991,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
                 for (int e = 0; e < 4; ++e) {
                     const int j = j0 + nt * 8 + tq * 2 + (e & 1);
                     const int i = e < 2 ? i_a : i_b;
-                    const float v = j <= i ? S[nt][e] * A.scale - r1 * __logf(1.0f + r2 * (float)(i - j)) : -INFINITY;
+                    const float v = j <= i ? S[nt][e] * A.scale - (penalty ? r1 * __logf(1.0f + r2 * (float)(i - j)) : 0.0f) : -INFINITY;
                     S[nt][e] = v;
                     if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                 }
@@ -995,12 +999,13 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            // without a sink a row of the tile's padding (beyond the sequence's rows) sees no key at all: keep its maximum finite
+            const float mn_a = fmaxf(fmaxf(m_a, mx_a), -1e30f), mn_b = fmaxf(fmaxf(m_b, mx_b), -1e30f);
             const float ca = __expf(m_a - mn_a), cb = __expf(m_b - mn_b);
             m_a = mn_a; m_b = mn_b;
             l_a *= ca; l_b *= cb;
 #pragma unroll
-            for (int nt = 0; nt < DP / 8; ++nt) { o[nt][0] *= ca; o[nt][1] *= ca; o[nt][2] *= cb; o[nt][3] *= cb; }
+            for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] *= ca; o[nt][1] *= ca; o[nt][2] *= cb; o[nt][3] *= cb; }
             uint32_t hi[8][2], lo[8][2];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
@@ -1018,9 +1023,9 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
 #pragma unroll
             for (int k2 = 0; k2 < 4; ++k2)
 #pragma unroll
-                for (int nt = 0; nt < DP / 8; ++nt) {
+                for (int nt = 0; nt < DV / 8; ++nt) {
                     uint32_t b0, b1;
-                    ldmatrix_x2_trans(b0, b1, Vt + (k2 * 16 + (lane & 15)) * LD + nt * 8);
+                    ldmatrix_x2_trans(b0, b1, Vt + (k2 * 16 + (lane & 15)) * LDV + nt * 8);
                     mma_bf16_16816(o[nt], hi[2 * k2][0], hi[2 * k2][1], hi[2 * k2 + 1][0], hi[2 * k2 + 1][1], b0, b1);
                     mma_bf16_16816(o[nt], lo[2 * k2][0], lo[2 * k2][1], lo[2 * k2 + 1][0], lo[2 * k2 + 1][1], b0, b1);
                 }
@@ -1032,15 +1037,14 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
     const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
-    const size_t goff = (size_t)A.H * A.d + A.G * A.d + A.G * A.dv + (size_t)h * A.dv;
 #pragma unroll
-    for (int nt = 0; nt < DP / 8; ++nt)
+    for (int nt = 0; nt < DV / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int row = e < 2 ? row_a : row_b, c = nt * 8 + tq * 2 + (e & 1);
             if (row < n && c < A.dv) {
                 const size_t t = t0 + row;
-                out[(t * A.H + h) * A.dv + c] = __float2bfloat16_rn(o[nt][e] * (e < 2 ? inv_a : inv_b) * sigmoidf_(A.proj[t * A.n_in + goff + c]));
+                out[(t * A.H + h) * A.dv + c] = __float2bfloat16_rn(o[nt][e] * (e < 2 ? inv_a : inv_b) * attn_gate(A, t, h, c));
             }
         }
 }
@@ -1530,7 +1534,7 @@ static cudaError_t scan_attribute() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * gla_buf_floats(DK) * sizeof(float)));
     return e;
 }
-static constexpr int flash_smem_bytes(int DP) { return 4 * 64 * (DP + 8) * (int)sizeof(bf16); }
+static constexpr int flash_smem_bytes(int DK, int DV, bool vk) { return 2 * 64 * ((DK + 8) + (vk ? 0 : DV + 8)) * (int)sizeof(bf16); }
 
 template <class T>
 static cudaError_t set_kernel_attributes() {
@@ -1541,7 +1545,9 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = scan_attribute<256>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128, 128, false));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 128, true));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 192, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 192, true));
     return e;
 }
 
@@ -1703,9 +1709,16 @@ static void launch_attention(SmolLm* m, const SmolLmStep* s, AttnArgs& A, bool f
             const bf16* qb = reinterpret_cast<const bf16*>(qbuf);
             const bf16* pl = reinterpret_cast<const bf16*>(pool);
             bf16* mx = reinterpret_cast<bf16*>(mix);
-            if (hp <= 32) attn_flash_kernel<32><<<grid, 128, flash_smem_bytes(32), st>>>(A, qb, pl, mx);
-            else if (hp <= 64) attn_flash_kernel<64><<<grid, 128, flash_smem_bytes(64), st>>>(A, qb, pl, mx);
-            else attn_flash_kernel<128><<<grid, 128, flash_smem_bytes(128), st>>>(A, qb, pl, mx);
+#define SMOL_FLASH(DK, DV, VK) attn_flash_kernel<DK, DV, VK><<<grid, 128, flash_smem_bytes(DK, DV, VK), st>>>(A, qb, pl, mx)
+            if (A.v_in_k) {
+                if (A.d <= 64) SMOL_FLASH(64, 64, true);
+                else if (A.d <= 128) SMOL_FLASH(128, 128, true);
+                else if (A.dv <= 128) SMOL_FLASH(192, 128, true);
+                else SMOL_FLASH(192, 192, true);
+            } else if (hp <= 32) SMOL_FLASH(32, 32, false);
+            else if (hp <= 64) SMOL_FLASH(64, 64, false);
+            else SMOL_FLASH(128, 128, false);
+#undef SMOL_FLASH
         } else {
             // every row, also those of short sequences
             const int au = Tn * A.H;
@@ -1814,8 +1827,9 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 A.k_ld = dk; A.v_ld = dk; A.v_in_k = 1;
                 A.gate_off = (size_t)L.q_rank + dk; A.gate_ld = 1; A.gate_step = 0;
                 A.q_norm = A.k_norm = A.r1 = A.r2 = A.sink = nullptr;
-                if (L.kv_rank <= 256) launch_attention<T, 8>(m, s, A, false, qbuf, pool, mix, st);
-                else launch_attention<T, 16>(m, s, A, false, qbuf, pool, mix, st);
+                const bool flash = sizeof(T) == 2 && dk <= 192;          // larger latents take the warp-per-row form for prompt portions
+                if (L.kv_rank <= 256) launch_attention<T, 8>(m, s, A, flash, qbuf, pool, mix, st);
+                else launch_attention<T, 16>(m, s, A, flash, qbuf, pool, mix, st);
                 // per head: the attended latent [Tn, kv_rank] times the value expansion [vdim, kv_rank]^T
                 GemmIo iv = plain_io(L.kv_rank, L.vdim);
                 iv.lda = L.heads * L.kv_rank; iv.ldy = L.heads * L.vdim;

@@ -499,20 +499,30 @@ constexpr int kTcThreads = 512;
 constexpr int kTcSmemBytes = umma::kRingBytes + 1024;
 constexpr int kTcMinRows = 257;          // below this the mma.sync tiles fill the GPU better than 128-row tiles
 
+// Grouped rows (io.tile_group != nullptr): the row tiles come from the device-built table (128 rows each, group g's rows end
+// at seg[g + 1]; rows of the tile beyond that belong to the next group and are computed but not stored), and group g's
+// weights are rows g * N .. of the weight map.
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                                                                float* __restrict__ y, int M, int N, int K) {
+                                                                float* __restrict__ y, int M, int N, int K, const GemmIo io) {
     extern __shared__ unsigned char tc_smem[];
     __shared__ umma::Bars bars;
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem) + 1023) & ~(uintptr_t)1023);
     umma::Pipe pipe;
     umma::setup(&bars, pipe, (uint32_t)umma::kAcc, 2u);
-    const int m_tiles = (M + umma::kM - 1) / umma::kM, n_tiles = (N + kTcTileN - 1) / kTcTileN;
+    const int m_tiles = io.tile_group ? *io.n_tiles : (M + umma::kM - 1) / umma::kM, n_tiles = (N + kTcTileN - 1) / kTcTileN;
     const int k_pad = (K + umma::kBK - 1) / umma::kBK * umma::kBK;
     const bool vec = N % 4 == 0;
     for (int u = blockIdx.x; u < m_tiles * n_tiles; u += gridDim.x) {
-        const int m0 = (u % m_tiles) * umma::kM, n0 = (u / m_tiles) * kTcTileN;
+        int m0 = (u % m_tiles) * umma::kM, w_row = 0;
+        const int n0 = (u / m_tiles) * kTcTileN;
+        if (io.tile_group) {
+            const int g = io.tile_group[u % m_tiles];
+            m0 = io.tile_row0[u % m_tiles];
+            M = io.seg[g + 1];
+            w_row = g * N;
+        }
         umma::BSrc b0, b1;
-        b0.tm = &tm_w; b0.row0 = n0; b0.n = kTcTileN; b0.box = kTcTileN;
+        b0.tm = &tm_w; b0.row0 = w_row + n0; b0.n = kTcTileN; b0.box = kTcTileN;
         b1.tm = nullptr; b1.row0 = 0; b1.n = 0; b1.box = kTcTileN;
         umma::tile_mma_tma<kTcThreads>(ring, &bars, pipe, k_pad, &tm_a, m0, b0, b1);
         umma::tile_epilogue(&bars, kTcTileN, [&](int row, int c0, const float (&acc)[8]) {
@@ -1351,7 +1361,7 @@ struct SmolLm {
     // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
     size_t o_hist = 0, o_cq = 0, o_qf = 0, o_qt = 0, o_qlat = 0, o_freq = 0;
-    size_t o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
+    size_t o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
     int max_cq = 0, max_qf = 0, max_qlat = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
     int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
@@ -1515,6 +1525,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
         m->o_zp = carve(T * (size_t)m->max_pair_ff * 2 * 4);
         m->o_actp = carve(T * (size_t)m->max_pair_ff * E);
         m->o_yp = carve(pairs * D * 4);
+        m->o_ap = carve(pairs * D * E);
     }
     m->total = o;
     *out = m;
@@ -1645,7 +1656,7 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
         if (smol::make_tensor_map_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)smol::umma::kM) &&
             smol::make_tensor_map_2d(&tw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)kTcTileN)) {
             const int tiles = ((M + smol::umma::kM - 1) / smol::umma::kM) * ((N + kTcTileN - 1) / kTcTileN);
-            gemm_tc_kernel<<<std::min(tiles, m->n_sms), kTcThreads, kTcSmemBytes, st>>>(ta, tw, y, M, N, K);
+            gemm_tc_kernel<<<std::min(tiles, m->n_sms), kTcThreads, kTcSmemBytes, st>>>(ta, tw, y, M, N, K, plain_io(K, N));
             m->launches++;
             return cudaGetLastError();
         }
@@ -1670,6 +1681,21 @@ cudaError_t linear<bf16>(SmolLm* m, const bf16* a, const bf16* w, float* y, int 
     }
     m->launches++;
     return cudaGetLastError();
+}
+
+// Grouped product on the tcgen05 tile: a [rows, K] sorted by group, w [groups * N, K], the table cut into 128-row tiles.
+// Returns false if this form does not apply (then the caller takes the mma.sync form with its own table).
+static bool linear_grouped_tc(SmolLm* m, const bf16* a, const bf16* w, float* y, int rows, int groups, int N, int K, const GemmIo& io,
+                              cudaStream_t st) {
+    const bool aligned = K % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0;
+    if (!(N >= kTcTileN && K >= smol::umma::kBK && aligned && m->tc_ready && reinterpret_cast<uintptr_t>(y) % 16 == 0)) return false;
+    CUtensorMap ta, tw;
+    if (!smol::make_tensor_map_2d(&ta, a, (uint64_t)rows, (uint64_t)K, (uint64_t)K, (uint32_t)smol::umma::kM) ||
+        !smol::make_tensor_map_2d(&tw, w, (uint64_t)groups * N, (uint64_t)K, (uint64_t)K, (uint32_t)kTcTileN))
+        return false;
+    gemm_tc_kernel<<<m->n_sms, kTcThreads, kTcSmemBytes, st>>>(ta, tw, y, rows, N, K, io);
+    m->launches++;
+    return true;
 }
 
 template <int DK>
@@ -1892,7 +1918,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 m->launches += 1;
             } else if (L.mlp == SMOL_LM_MLP_GATED) {
                 CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, 2 * L.ff, D, st));
-                gated_act_kernel<T><<<cast_grid((size_t)Tn * L.ff), 256, 0, st>>>(z, L.ff, L.mlp_act, (size_t)Tn, act);
+                gated_act_kernel<T><<<cast_grid((size_t)Tn * L.ff / 4), 256, 0, st>>>(z, L.ff, L.mlp_act, (size_t)Tn, act);
                 CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
                 m->launches += 1;
             } else if (L.mlp == SMOL_LM_MLP_EXPERTS) {
@@ -1916,17 +1942,46 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 else moe_route_kernel<T><<<Tn, 128, 0, st>>>(Rt, hn, sel_id, sel_w);
                 m->launches += 1;
                 if (L.n_experts > 0) {
-                    moe_index_kernel<<<1, 256, 0, st>>>(sel_id, pairs, L.n_experts, kGroupTile, seg, perm, slot_of, tile_g, tile_r, n_tiles);
+                    // three forms of the two grouped products, by how many rows an expert gets: a warp per output column for
+                    // a handful of pairs (decoding), 32-row mma.sync tiles, 128-row tcgen05 tiles over rows copied into sorted order
+                    const bool few = !kIsF32 && pairs <= kMoeGemvPairs && D % 8 == 0 && L.ff % 8 == 0;
+                    const bool big = !kIsF32 && !few && m->tc_ready && pairs / L.n_experts >= 64 && D % 8 == 0 && L.ff % 8 == 0 &&
+                                     2 * L.ff >= kTcTileN && D >= kTcTileN && D >= smol::umma::kBK && L.ff >= smol::umma::kBK;
+                    const int tile_rows = big ? smol::umma::kM : kGroupTile;
+                    moe_index_kernel<<<1, 256, 0, st>>>(sel_id, pairs, L.n_experts, tile_rows, seg, perm, slot_of, tile_g, tile_r, n_tiles);
                     const int tiles = pairs / kGroupTile + L.n_experts;
                     GemmIo io = plain_io(D, 2 * L.ff);
                     io.sw = (long long)2 * L.ff * D;
-                    io.tile_group = tile_g; io.tile_row0 = tile_r; io.seg = seg; io.n_tiles = n_tiles; io.gather = perm; io.gather_div = L.top_k;
-                    CU(linear_ex<T>(m, hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
-                    gated_act_kernel<T><<<cast_grid((size_t)pairs * L.ff), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
+                    io.tile_group = tile_g; io.tile_row0 = tile_r; io.seg = seg; io.n_tiles = n_tiles;
                     GemmIo io2 = plain_io(L.ff, D);
                     io2.sw = (long long)D * L.ff;
                     io2.tile_group = tile_g; io2.tile_row0 = tile_r; io2.seg = seg; io2.n_tiles = n_tiles;
-                    CU(linear_ex<T>(m, actp, static_cast<const T*>(L.w_experts_out), yp, pairs, D, L.ff, io2, 1, tiles, st));
+                    const size_t act_n = (size_t)pairs * L.ff;
+                    if (few) {
+                        const bf16* hb = reinterpret_cast<const bf16*>(hn);
+                        moe_gemv_kernel<<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(hb, perm, L.top_k, sel_id, seg + L.n_experts,
+                                                                                         reinterpret_cast<const bf16*>(L.w_experts_in), io.sw, zp, 2 * L.ff, D);
+                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
+                        moe_gemv_kernel<<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(reinterpret_cast<const bf16*>(actp), perm, 0, sel_id, seg + L.n_experts,
+                                                                                   reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
+                        m->launches += 2;
+                    } else {
+                        bool done = false;
+                        if (big) {
+                            bf16* ap = reinterpret_cast<bf16*>(m->ws + m->o_ap);
+                            moe_gather_kernel<<<pairs, 128, 0, st>>>(reinterpret_cast<const bf16*>(hn), perm, L.top_k, seg + L.n_experts, D, ap);
+                            m->launches++;
+                            done = linear_grouped_tc(m, ap, reinterpret_cast<const bf16*>(L.w_experts_in), zp, pairs, L.n_experts, 2 * L.ff, D, io, st);
+                        }
+                        if (!done) {
+                            io.gather = perm; io.gather_div = L.top_k;
+                            CU(linear_ex<T>(m, hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
+                        }
+                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
+                        if (!(big && linear_grouped_tc(m, reinterpret_cast<const bf16*>(actp), reinterpret_cast<const bf16*>(L.w_experts_out), yp, pairs,
+                                                       L.n_experts, D, L.ff, io2, st)))
+                            CU(linear_ex<T>(m, actp, static_cast<const T*>(L.w_experts_out), yp, pairs, D, L.ff, io2, 1, tiles, st));
+                    }
                     m->launches += 2;
                 } else {
                     CU(cudaMemsetAsync(slot_of, 0xff, (size_t)pairs * 4, st));

@@ -280,26 +280,41 @@ __global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_sc
         const float* b = sh + cur * kBuf;
         const float4* s4 = reinterpret_cast<const float4*>(b) + q;      // piece e of a vector of token tt: s4[(tt*DK)/4 + e*L]
         const float* s_v = b + 3 * PL + col;
-        for (int tt = 0; tt < n; ++tt) {
-            const float v = s_v[tt * CB];
-            float sa = 0.0f, sb = 0.0f;
+        // four tokens at a time: their state updates follow one another, their sums over the key rows are then reduced side
+        // by side, so that the shuffle latency is paid once per four tokens
+        for (int tt = 0; tt < n; tt += 4) {
+            float po[4];
 #pragma unroll
-            for (int e = 0; e < RV; ++e) {
-                const float4* p = s4 + tt * (DK / 4) + e * L;
-                const float4 qv = p[0], kv = p[PL / 4], wv = p[2 * (PL / 4)];
-                S[e][0] = fmaf(wv.x, S[e][0], kv.x * v);
-                S[e][1] = fmaf(wv.y, S[e][1], kv.y * v);
-                S[e][2] = fmaf(wv.z, S[e][2], kv.z * v);
-                S[e][3] = fmaf(wv.w, S[e][3], kv.w * v);
-                sa = fmaf(S[e][0], qv.x, sa);
-                sb = fmaf(S[e][1], qv.y, sb);
-                sa = fmaf(S[e][2], qv.z, sa);
-                sb = fmaf(S[e][3], qv.w, sb);
+            for (int u = 0; u < 4; ++u) {
+                po[u] = 0.0f;
+                if (tt + u < n) {
+                    const float v = s_v[(tt + u) * CB];
+                    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < RV; ++e) {
+                        const float4* p = s4 + (tt + u) * (DK / 4) + e * L;
+                        const float4 qv = p[0], kv = p[PL / 4], wv = p[2 * (PL / 4)];
+                        S[e][0] = fmaf(wv.x, S[e][0], kv.x * v);
+                        S[e][1] = fmaf(wv.y, S[e][1], kv.y * v);
+                        S[e][2] = fmaf(wv.z, S[e][2], kv.z * v);
+                        S[e][3] = fmaf(wv.w, S[e][3], kv.w * v);
+                        sa = fmaf(S[e][0], qv.x, sa);
+                        sb = fmaf(S[e][1], qv.y, sb);
+                        sa = fmaf(S[e][2], qv.z, sa);
+                        sb = fmaf(S[e][3], qv.w, sb);
+                    }
+                    po[u] = sa + sb;
+                }
             }
-            float po = sa + sb;
 #pragma unroll
-            for (int s = 1; s < L; s <<= 1) po += __shfl_xor_sync(0xffffffffu, po, s);
-            if (q == 0 && j < dv) o_raw[(size_t)(c0 + tt) * A.H * dv + h * dv + j] = po * A.q_scale;
+            for (int s = 1; s < L; s <<= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) po[u] += __shfl_xor_sync(0xffffffffu, po[u], s);
+            if (q == 0 && j < dv) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (tt + u < n) o_raw[(size_t)(c0 + tt + u) * A.H * dv + h * dv + j] = po[u] * A.q_scale;
+            }
         }
     }
 #pragma unroll
@@ -332,6 +347,16 @@ __global__ void gla_out_kernel(const GlaArgs A, const float* __restrict__ o_raw,
 // Gated feed-forward: z rows hold gate [F] | up [F]; out = act(gate) * up in T.
 template <class T>
 __global__ void gated_act_kernel(const float* __restrict__ z, int F, int kind, size_t rows, T* __restrict__ out) {
+    if (F % 4 == 0) {                      // 16-byte pieces
+        const size_t n = rows * (F / 4);
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t r = i / (F / 4), c = (i - r * (F / 4)) * 4;
+            const float4 g = *reinterpret_cast<const float4*>(z + r * 2 * F + c), u = *reinterpret_cast<const float4*>(z + r * 2 * F + F + c);
+            store4<T>(out + r * F + c, gated_act_(kind, g.x) * u.x, gated_act_(kind, g.y) * u.y, gated_act_(kind, g.z) * u.z,
+                      gated_act_(kind, g.w) * u.w);
+        }
+        return;
+    }
     const size_t n = rows * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / F, c = i - r * F;
@@ -463,6 +488,47 @@ __global__ void __launch_bounds__(256) moe_index_kernel(const int32_t* __restric
         }
         slot_of[p] = slot;
     }
+}
+
+// Rows of the sorted order copied next to each other (the tcgen05 tile reads its rows through one tensor map): row r is
+// the input row of pair perm[r].  One block per row; rows beyond the sorted pairs (*n_sorted) are left alone.
+__global__ void moe_gather_kernel(const bf16* __restrict__ h, const int32_t* __restrict__ perm, int div, const int32_t* __restrict__ n_sorted,
+                                  int D, bf16* __restrict__ out) {
+    const int r = blockIdx.x;
+    if (r >= *n_sorted) return;
+    const bf16* src = h + (size_t)(perm[r] / div) * D;
+    bf16* dst = out + (size_t)r * D;
+    if (D % 8 == 0) {
+        for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+    } else {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+// The grouped product for a handful of rows (decoding): one warp per (sorted row, output column), lanes cut K into 16-byte
+// pieces, the expert's weight row is streamed once.  Sorted row r belongs to pair perm[r], whose router output names the
+// expert; it reads a's row perm[r] / gather_div (gather_div == 0: row r itself).  Needs K % 8 == 0 and 16-byte aligned rows.
+constexpr int kMoeGemvPairs = 32;
+__global__ void __launch_bounds__(256) moe_gemv_kernel(const bf16* __restrict__ a, const int32_t* __restrict__ perm, int gather_div,
+                                                       const int32_t* __restrict__ sel_id, const int32_t* __restrict__ n_sorted,
+                                                       const bf16* __restrict__ w, long long w_stride, float* __restrict__ y, int N, int K) {
+    const int r = blockIdx.y;
+    if (r >= *n_sorted) return;
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const int pair = perm[r];
+    const bf16* wr = w + (long long)sel_id[pair] * w_stride + (size_t)n * K;
+    const bf16* ar = a + (size_t)(gather_div > 0 ? pair / gather_div : r) * K;
+    float acc = 0.0f;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = ldg_stream(wr + k), av = ldg_v4(ar + k);
+        acc = fmaf(bf_lo(av.x), bf_lo(wv.x), acc); acc = fmaf(bf_hi(av.x), bf_hi(wv.x), acc);
+        acc = fmaf(bf_lo(av.y), bf_lo(wv.y), acc); acc = fmaf(bf_hi(av.y), bf_hi(wv.y), acc);
+        acc = fmaf(bf_lo(av.z), bf_lo(wv.z), acc); acc = fmaf(bf_hi(av.z), bf_hi(wv.z), acc);
+        acc = fmaf(bf_lo(av.w), bf_lo(wv.w), acc); acc = fmaf(bf_hi(av.w), bf_hi(wv.w), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)r * N + n] = acc;
 }
 
 // y[t] = sum_k w[t][k] * (expert output of pair (t, k), or the input x[t] for an identity output), k ascending.

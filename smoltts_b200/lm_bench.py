@@ -1,5 +1,6 @@
-"""Prefill and decode throughput of the hybrid language-model engine at layer sizes that resemble a real model's,
-beside the DualAR slow transformer (the package's closest model: attention + gated MLP layers) at equal size.
+"""Prefill and decode throughput of the hybrid language-model engine at layer sizes that resemble a real model's:
+the Pamasun design beside the DualAR slow transformer (the package's closest model: attention + gated MLP layers), and the
+Maferax design beside Pamasun at equal width, depth, head count and layer pattern (``--lm-design maferax``).
 
 ``python bench.py --lm`` prints one JSON line: for every size, tokens/s of a whole-prompt prefill and of single-token
 decode steps against a filled cache, each with its distance from the roofline (matrix-product + attention flops over the
@@ -22,6 +23,120 @@ SIZES = {
     "w1536": dict(width=1536, layers=12, heads=12, kv_heads=4, dim=128, ff=6144, vocab=8192, pattern="daa"),
     "w768attn": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, ff=4608, vocab=2368, pattern="a"),
 }
+
+
+MAFERAX_SIZES = {
+    # recurrence: heads x (dim keys, vdim values); latent attention: heads x (dim + rot | vdim) through latents q_rank / kv_rank;
+    # feed-forward: dense gated (ff) on recurrent layers, routed experts on attention layers (top of experts, expert size eff)
+    "w768": dict(width=768, layers=10, heads=12, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=128, ff=3072, experts=16, identity=2, top=3,
+                 groups=3, keep=2, eff=1024, vocab=2368, pattern="gll"),
+    "w1536": dict(width=1536, layers=12, heads=12, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=128, ff=4096, experts=32, identity=4, top=4,
+                  groups=4, keep=2, eff=1024, vocab=8192, pattern="gll"),
+    "w768dense": dict(width=768, layers=10, heads=12, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=128, ff=3072, experts=0, identity=0, top=0,
+                      groups=1, keep=1, eff=0, vocab=2368, pattern="gll"),
+}
+
+
+def maferax_config(width, layers, heads, dim, rot, vdim, q_rank, kv_rank, ff, experts, identity, top, groups, keep, eff, vocab, pattern) -> dict:
+    ls = []
+    for i in range(layers):
+        if pattern[i % len(pattern)] == "l":
+            mlp = ({"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": identity, "top": top,
+                                                                    "groups": {"count": groups, "keep": keep}, "scale": 2.0}}
+                   if experts else {"kind": "dense", "ff": ff})
+            ls.append({"type": "latent_attention", "mlp": mlp,
+                       "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+                                 "scale": (dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}})
+        else:
+            ls.append({"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": 16.0}, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Maferax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "logit_scale": 1.0, "layers": ls}
+
+
+def maferax_state_dict(cfg, seed: int = 0, rank: int = 16) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for k, s in cfg.tensor_shapes({i: rank for i in range(len(cfg.layers))}).items():
+        if len(s) == 2:
+            sd[k] = (torch.randn(*s, generator=g) * (s[1] ** -0.5)).bfloat16()
+        elif len(s) == 0:
+            sd[k] = torch.ones(()).bfloat16()
+        elif k.endswith("dwa"):
+            sd[k] = torch.cat([torch.full((s[0] - 1,), 0.1), torch.ones(1)]).bfloat16()
+        elif k.endswith(("dq.norm", "dkv.norm", "mix.norm")):
+            sd[k] = torch.ones(s).bfloat16()
+        elif k.endswith("a2.b"):
+            sd[k] = torch.full(s, 3.0).bfloat16()
+        else:
+            sd[k] = (torch.randn(*s, generator=g) * 0.05).bfloat16()
+    sd["embed"] = torch.randn(*sd["embed"].shape, generator=g).bfloat16()
+    return sd
+
+
+def bench_maferax(name: str, prompt: int, batch: int, decode_steps: int, warmup: int, steps: int, peaks) -> dict:
+    """Like bench_pamasun.  Prefill flops: matrix products of the weights one token touches, attention in the latent space
+    (per visible key 2 (kv_rank + rot) + 2 kv_rank flops per head) and the recurrence (6 dim vdim per head); decode bytes:
+    the weights one step touches (every expert only if the batch's choices can cover them all), the latent cache and the states."""
+    from .lm import MaferaxLM
+    from .lm_config import MaferaxConfig
+
+    hbm, tflops, _ = peaks
+    spec = MAFERAX_SIZES[name]
+    cfg = MaferaxConfig.from_dict(maferax_config(**spec))
+    rank = 16
+    model = MaferaxLM(cfg, dtype=torch.bfloat16, max_tokens=batch * (prompt + 64 + decode_steps), max_seqs=batch, page_size=64,
+                      max_step_tokens=2048, max_want=batch)
+    model.load_state_dict(maferax_state_dict(cfg, 0, rank))
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (batch, prompt + decode_steps), generator=g).tolist()
+    n_attn = sum(L.mixer.kind == "latent_attention" for L in cfg.layers)
+    n_rec = len(cfg.layers) - n_attn
+    H, d, dv, kr, rot = spec["heads"], spec["dim"], spec["vdim"], spec["kv_rank"], spec["rot"]
+    mm_flops = cfg.matmul_flops_per_token(rank) - 2 * cfg.vocab * cfg.width
+
+    def prefill():
+        seq = model.open_sequence()
+        for lo in range(0, prompt, model.max_step_tokens):
+            part = toks[0][lo:min(prompt, lo + model.max_step_tokens)]
+            model.forward([(seq, part, [len(part) - 1] if lo + len(part) == prompt else [])])
+        model.close_sequence(seq)
+
+    l0 = model.launch_count
+    ms_p = _timed(prefill, warmup, steps)
+    launches = model.launch_count - l0
+    flops_p = prompt * mm_flops + n_attn * H * (4 * kr + 2 * rot) * prompt * (prompt + 1) / 2 + n_rec * 6 * H * d * dv * prompt
+    seqs = [model.open_sequence() for _ in range(batch)]
+    for b, s in enumerate(seqs):
+        for lo in range(0, prompt, model.max_step_tokens):
+            model.forward([(s, toks[b][lo:min(prompt, lo + model.max_step_tokens)], [])])
+
+    def decode():
+        for i in range(decode_steps):
+            model.forward([(s, [toks[b][prompt + i]], [0]) for b, s in enumerate(seqs)])
+        for s in seqs:
+            s.length = prompt
+
+    l0 = model.launch_count
+    ms_d = _timed(decode, 2, steps) / decode_steps
+    launches += model.launch_count - l0
+    ctx = prompt + decode_steps / 2
+    # weights a decode step reads: everything but the experts, plus min(batch * top, experts) experts per routed layer
+    all_w, act_w = cfg.weight_elements(rank), cfg.weight_elements(rank, active_only=True)
+    touched = act_w
+    if spec["experts"]:
+        per_expert = (all_w - act_w) / max(spec["experts"] - spec["top"], 1)
+        touched = all_w - per_expert * max(spec["experts"] - min(batch * spec["top"], spec["experts"]), 0)
+    kv_bytes = n_attn * (kr + rot) * 2 * ctx * batch
+    st_bytes = n_rec * 2 * H * d * dv * 4 * batch
+    bytes_d = 2 * touched + kv_bytes + st_bytes
+    model.check_device_errors()
+    for s in seqs:
+        model.close_sequence(s)
+    return {"model": f"Maferax {name}", "spec": spec, "parameters_m": round(all_w / 1e6, 1), "active_parameters_m": round(act_w / 1e6, 1),
+            "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
+                        "of_peak": flops_p / ms_p / 1e9 / tflops},
+            "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
+                       "gbs": bytes_d / ms_d / 1e6, "of_peak": bytes_d / ms_d / 1e6 / hbm},
+            "gpu_launches": int(launches)}
 
 
 def pamasun_config(width, layers, heads, kv_heads, dim, ff, vocab, pattern) -> dict:
@@ -193,14 +308,24 @@ def bench_dualar(prompt: int, batch: int, decode_steps: int, warmup: int, steps:
 def run(args, root: str) -> None:
     assert torch.cuda.is_available(), "the language-model benchmark needs a CUDA device"
     peaks = _peaks(root)
-    names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768attn", "w1536"])]
     t0 = time.time()
     entries: List[dict] = []
-    for n in names:
+    if getattr(args, "lm_design", "pamasun") == "maferax":
+        # Maferax beside Pamasun (the engine's closest design) at equal width, depth, heads and layer pattern
+        names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768dense", "w1536"])]
+        for n in names:
+            for batch in (1, 4):
+                entries.append(bench_maferax(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+        for n in sorted({"w1536" if n == "w1536" else "w768" for n in names}):
+            for batch in (1, 4):
+                entries.append(bench_pamasun(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+    else:
+        names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768attn", "w1536"])]
+        for n in names:
+            for batch in (1, 4):
+                entries.append(bench_pamasun(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
         for batch in (1, 4):
-            entries.append(bench_pamasun(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
-    for batch in (1, 4):
-        entries.append(bench_dualar(args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+            entries.append(bench_dualar(args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
     print(json.dumps({"metric": "language-model prefill and decode tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
                       "peaks": {"hbm_gbs": peaks[0], "bf16_tflops": peaks[1], "source": peaks[2]}, "steps": args.steps,
                       "warmup": args.warmup, "entries": entries, "gpu_launches": sum(e["gpu_launches"] for e in entries),

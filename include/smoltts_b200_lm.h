@@ -76,13 +76,14 @@ typedef struct SmolLmLayer {
     const float *act;                               /* PolyNorm coefficients a, b, c, e */
     /* --- latent attention, gated linear recurrence, gated and routed feed-forwards --- */
     int32_t rot_dim;          /* latent attention: rotated query/key coordinates per head (after the `dim` unrotated ones) */
+    int32_t rot_dims;         /* of these, the leading coordinates the rotation acts on (even, <= rot_dim; the rest pass unchanged) */
     int32_t q_rank, kv_rank;  /* latent attention: sizes of the query latent and of the cached key/value latent */
     int32_t mlp_act;          /* SMOL_LM_ACT_* of a gated feed-forward or of the experts */
     int32_t n_experts;        /* routed: experts with weights */
     int32_t n_identity;       /* routed: further router outputs whose "expert" returns its input */
     int32_t top_k;            /* routed: router outputs used per token */
     int32_t n_groups, keep_groups;  /* routed: outputs form n_groups equal groups of neighbours, chosen from the best keep_groups */
-    float rot_base;           /* rotation angle of pair i at position p: p * rot_base^(-2i / rot_dim) */
+    float rot_base;           /* rotation angle of pair i at position p: p * rot_base^(-2i / rot_dims) */
     float decay_tau;          /* gated linear: decay = sigmoid(z)^(1 / decay_tau) */
     float router_scale;       /* routed: multiplies the normalised weights */
     /* latent attention: w_in rows are query-latent [q_rank] | key/value latent [kv_rank] | shared rotated key [rot_dim] | gate [heads];

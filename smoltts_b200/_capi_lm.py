@@ -21,7 +21,7 @@ class SmolLmLayer(C.Structure):
         (n, C.c_void_p) for n in ("w_in", "w_out", "w_up", "w_down", "norm1", "norm1b", "norm2", "norm2b", "ls1", "ls2",
                                   "q_norm", "k_norm", "dist_r1", "dist_r2", "sink", "rate_bias", "decay_w2", "decay_bias",
                                   "out_norm", "act")] + [
-        (n, C.c_int32) for n in ("rot_dim", "q_rank", "kv_rank", "mlp_act", "n_experts", "n_identity", "top_k", "n_groups", "keep_groups")] + [
+        (n, C.c_int32) for n in ("rot_dim", "rot_dims", "q_rank", "kv_rank", "mlp_act", "n_experts", "n_identity", "top_k", "n_groups", "keep_groups")] + [
         (n, C.c_float) for n in ("rot_base", "decay_tau", "router_scale")] + [
         (n, C.c_void_p) for n in ("w_q_up", "w_k_up_t", "w_v_up", "q_lat_norm", "kv_lat_norm", "w_experts_in", "w_experts_out", "w_router",
                                   "route_bias", "depth_mix")]

@@ -226,11 +226,14 @@ __global__ void polynorm_kernel(const float* __restrict__ z, const float* __rest
 //  - grouped rows (tile_group != nullptr): the rows are sorted by group (expert), group g owning rows seg[g] .. seg[g+1]-1
 //    and the weight matrix w + g * sw; blockIdx.y walks a tile table built on the device (tiles beyond *n_tiles leave at
 //    once), and row r of the sorted order reads a's row gather[r] / gather_div (gather == nullptr: row r itself).
+//  - bf16 products only: a_f32 -- a holds fp32 and is rounded to bf16 as it is staged; y_bf16 -- y holds bf16 (a result that
+//    feeds the next product directly).
 struct GemmIo {
     int lda, ldy;
     long long sa, sw, sy;
     const int32_t *tile_group, *tile_row0, *seg, *n_tiles, *gather;
     int gather_div;
+    int a_f32, y_bf16;
 };
 constexpr int kGroupTile = 32;     // rows per tile of a grouped product (the tile table is built for this height)
 static GemmIo plain_io(int K, int N) {
@@ -238,6 +241,7 @@ static GemmIo plain_io(int K, int N) {
     io.lda = K; io.ldy = N; io.sa = io.sw = io.sy = 0;
     io.tile_group = io.tile_row0 = io.seg = io.n_tiles = io.gather = nullptr;
     io.gather_div = 1;
+    io.a_f32 = io.y_bf16 = 0;
     return io;
 }
 
@@ -313,12 +317,23 @@ constexpr int kGemmLd = kGemmBK + 8;   // 80-byte rows: fragment loads hit 32 di
 // off[i]: element offset of the i-th row this thread fetches (negative: a row outside the matrix, read as zeros)
 template <int ROWS>
 __device__ __forceinline__ void gemm_fetch(const bf16* __restrict__ src, const long long (&off)[ROWS * 4 / 128], int K, int k0, bool vec,
-                                           uint4 (&reg)[ROWS * 4 / 128]) {
+                                           uint4 (&reg)[ROWS * 4 / 128], bool f32 = false) {
 #pragma unroll
     for (int i = 0; i < ROWS * 4 / 128; ++i) {
         const int c = (threadIdx.x & 3) * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (off[i] >= 0) {
+        if (off[i] >= 0 && f32) {
+            const float* p = reinterpret_cast<const float*>(src) + off[i] + k0 + c;
+            float e[8];
+            if (vec && k0 + c + 8 <= K) {
+                const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+                e[0] = lo.x; e[1] = lo.y; e[2] = lo.z; e[3] = lo.w; e[4] = hi.x; e[5] = hi.y; e[6] = hi.z; e[7] = hi.w;
+            } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) e[x] = (k0 + c + x < K) ? p[x] : 0.0f;
+            }
+            v = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+        } else if (off[i] >= 0) {
             const bf16* p = src + off[i] + k0 + c;
             if (vec && k0 + c + 8 <= K) {
                 v = *reinterpret_cast<const uint4*>(p);
@@ -353,9 +368,10 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
     __shared__ __align__(16) bf16 Ws[2][BN * kGemmLd];
     int m0 = blockIdx.y * BM;
     const int n0 = blockIdx.x * BN;
-    a += blockIdx.z * io.sa;
+    const bool af = io.a_f32 != 0;
+    a = af ? reinterpret_cast<const bf16*>(reinterpret_cast<const float*>(a) + blockIdx.z * io.sa) : a + blockIdx.z * io.sa;
     w += blockIdx.z * io.sw;
-    y += blockIdx.z * io.sy;
+    const size_t y_base = (size_t)blockIdx.z * io.sy;
     if (io.tile_group) {
         if ((int)blockIdx.y >= *io.n_tiles) return;
         const int g = io.tile_group[blockIdx.y];
@@ -384,7 +400,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
         const int n = n0 + ((threadIdx.x + i * 128) >> 2);
         ow[i] = n < N ? (long long)n * K : -1;
     }
-    gemm_fetch<BM>(a, oa, K, 0, vec, ra);
+    gemm_fetch<BM>(a, oa, K, 0, vec, ra, af);
     gemm_fetch<BN>(w, ow, K, 0, vec, rw);
     gemm_stash<BM>(As[0], ra);
     gemm_stash<BN>(Ws[0], rw);
@@ -393,7 +409,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
     for (int s = 0; s < steps; ++s) {
         const int cur = s & 1;
         if (s + 1 < steps) {
-            gemm_fetch<BM>(a, oa, K, (s + 1) * kGemmBK, vec, ra);
+            gemm_fetch<BM>(a, oa, K, (s + 1) * kGemmBK, vec, ra, af);
             gemm_fetch<BN>(w, ow, K, (s + 1) * kGemmBK, vec, rw);
         }
 #pragma unroll
@@ -432,7 +448,11 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const bf16* __restrict__
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int mm = m + (e >> 1) * 8, nn = n + (e & 1);
-                if (mm < M && nn < N) y[(size_t)mm * io.ldy + nn] = acc[i][j][e];
+                if (mm < M && nn < N) {
+                    const size_t at = y_base + (size_t)mm * io.ldy + nn;
+                    if (io.y_bf16) reinterpret_cast<bf16*>(y)[at] = __float2bfloat16_rn(acc[i][j][e]);
+                    else y[at] = acc[i][j][e];
+                }
             }
         }
 }
@@ -1360,7 +1380,7 @@ struct SmolLm {
     size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_oraw, o_q, o_hw, o_err, o_part, total;
     // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
-    size_t o_hist = 0, o_cq = 0, o_qf = 0, o_qt = 0, o_qlat = 0, o_freq = 0;
+    size_t o_hist = 0, o_cq = 0, o_qf = 0, o_freq = 0;
     size_t o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
     int max_cq = 0, max_qf = 0, max_qlat = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
@@ -1430,16 +1450,16 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_hd = std::max(m->max_hd, L.heads * L.dim);
             m->max_mix = std::max(m->max_mix, L.heads * L.dim);
         } else if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
-            if (L.vdim < 1 || L.q_rank < 1 || L.kv_rank < 1 || L.rot_dim < 0 || L.rot_dim % 2) {
+            if (L.vdim < 1 || L.q_rank < 1 || L.kv_rank < 1 || L.rot_dim < 0 || L.rot_dims < 0 || L.rot_dims > L.rot_dim || L.rot_dims % 2) {
                 delete m;
-                return fail(SMOL_ERR_INVALID, "latent attention: vdim, q_rank, kv_rank must be positive and rot_dim even");
+                return fail(SMOL_ERR_INVALID, "latent attention: vdim, q_rank, kv_rank must be positive, rot_dims even and at most rot_dim");
             }
             if (L.kv_rank > 32 * kAttnMaxV) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "latent attention: latent size above 512"); }
             // a cached position: the latent, then the shared rotated key part; keys and values are the same row
             r.k_off = r.v_off = m->page_elems;
             m->page_elems += (size_t)cfg->page_size * (L.kv_rank + L.rot_dim);
             r.freq_off = m->freq_table.size();
-            for (int i = 0; i < L.rot_dim / 2; ++i) m->freq_table.push_back((float)pow((double)L.rot_base, -2.0 * i / (double)L.rot_dim));
+            for (int i = 0; i < L.rot_dims / 2; ++i) m->freq_table.push_back((float)pow((double)L.rot_base, -2.0 * i / (double)L.rot_dims));
             m->max_q = std::max(m->max_q, L.heads * (L.kv_rank + L.rot_dim));
             m->max_heads = std::max(m->max_heads, L.heads);
             m->max_vdim = std::max(m->max_vdim, L.kv_rank);
@@ -1508,8 +1528,6 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     if (m->max_cq > 0) {
         m->o_cq = carve(T * (size_t)m->max_cq * E);
         m->o_qf = carve(T * (size_t)m->max_qf * 4);
-        m->o_qt = carve(T * (size_t)m->max_qf * E);
-        m->o_qlat = carve(T * (size_t)m->max_qlat * 4);
         m->o_freq = carve(m->freq_table.size() * 4 + 4);
     }
     if (m->max_top > 0) {
@@ -1623,7 +1641,8 @@ cudaError_t linear<float>(SmolLm* m, const float* a, const float* w, float* y, i
 }
 
 static bool io_vec(const void* a, const void* w, int K, const GemmIo& io) {
-    return K % 8 == 0 && io.lda % 8 == 0 && io.sa % 8 == 0 && io.sw % 8 == 0 &&
+    const int ea = io.a_f32 ? 4 : 8;       // elements of a in 16 bytes
+    return K % 8 == 0 && io.lda % ea == 0 && io.sa % ea == 0 && io.sw % 8 == 0 &&
            (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0;
 }
 
@@ -1827,10 +1846,8 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 const int dk = L.kv_rank + L.rot_dim, qw = L.dim + L.rot_dim;
                 T* cq = reinterpret_cast<T*>(m->ws + m->o_cq);
                 float* qf = reinterpret_cast<float*>(m->ws + m->o_qf);
-                T* qt = kIsF32 ? reinterpret_cast<T*>(qf) : reinterpret_cast<T*>(m->ws + m->o_qt);
-                float* qlat = reinterpret_cast<float*>(m->ws + m->o_qlat);
                 LatentArgs P;
-                P.proj = proj; P.n_in = n_in; P.q_rank = L.q_rank; P.kv_rank = L.kv_rank; P.rot = L.rot_dim; P.H = L.heads; P.d = L.dim;
+                P.proj = proj; P.n_in = n_in; P.q_rank = L.q_rank; P.kv_rank = L.kv_rank; P.rot = L.rot_dim; P.rot_pairs = L.rot_dims / 2; P.H = L.heads; P.d = L.dim;
                 P.eps = c.norm_eps; P.q_lat_norm = L.q_lat_norm; P.kv_lat_norm = L.kv_lat_norm;
                 P.freq = reinterpret_cast<const float*>(m->ws + m->o_freq) + R.freq_off;
                 P.tok_seq = s->tok_seq; P.tok_pos = s->tok_pos; P.block_table = s->block_table;
@@ -1838,16 +1855,15 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 P.page_elems = m->page_elems; P.k_off = R.k_off; P.err = err;
                 latent_prep_kernel<T><<<Tn, 128, 0, st>>>(P, cq, pool);
                 CU(linear<T>(m, cq, static_cast<const T*>(L.w_q_up), qf, Tn, L.heads * qw, L.q_rank, st));
-                if (!kIsF32) {
-                    cast_kernel<T><<<cast_grid((size_t)Tn * L.heads * qw), 256, 0, st>>>(qf, qt, (size_t)Tn * L.heads * qw);
-                    m->launches++;
-                }
-                // per head: the unrotated query [Tn, dim] times the transposed key expansion [kv_rank, dim]^T
+                // per head: the unrotated query [Tn, dim] times the transposed key expansion [kv_rank, dim]^T, written where
+                // the attention reads its queries (bf16 engine: read from the fp32 q, written in bf16)
                 GemmIo io = plain_io(L.dim, L.kv_rank);
-                io.lda = L.heads * qw; io.ldy = L.heads * L.kv_rank;
-                io.sa = qw; io.sw = (long long)L.kv_rank * L.dim; io.sy = L.kv_rank;
-                CU(linear_ex<T>(m, qt, static_cast<const T*>(L.w_k_up_t), qlat, Tn, L.kv_rank, L.dim, io, L.heads, 0, st));
-                latent_query_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(P, qf, qlat, qbuf);
+                io.lda = L.heads * qw; io.ldy = L.heads * dk;
+                io.sa = qw; io.sw = (long long)L.kv_rank * L.dim; io.sy = dk;
+                io.a_f32 = io.y_bf16 = kIsF32 ? 0 : 1;
+                CU(linear_ex<T>(m, reinterpret_cast<const T*>(qf), static_cast<const T*>(L.w_k_up_t), reinterpret_cast<float*>(qbuf), Tn, L.kv_rank,
+                                L.dim, io, L.heads, 0, st));
+                latent_query_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(P, qf, qbuf);
                 m->launches += 2;
                 A.G = 1; A.d = dk; A.dv = L.kv_rank;
                 A.k_ld = dk; A.v_ld = dk; A.v_in_k = 1;
@@ -1860,14 +1876,11 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 GemmIo iv = plain_io(L.kv_rank, L.vdim);
                 iv.lda = L.heads * L.kv_rank; iv.ldy = L.heads * L.vdim;
                 iv.sa = L.kv_rank; iv.sw = (long long)L.vdim * L.kv_rank; iv.sy = L.vdim;
-                CU(linear_ex<T>(m, mix, static_cast<const T*>(L.w_v_up), oraw, Tn, L.vdim, L.kv_rank, iv, L.heads, 0, st));
+                iv.y_bf16 = kIsF32 ? 0 : 1;
+                T* expanded = reinterpret_cast<T*>(oraw);          // [Tn, heads * vdim] in T
+                CU(linear_ex<T>(m, mix, static_cast<const T*>(L.w_v_up), reinterpret_cast<float*>(expanded), Tn, L.vdim, L.kv_rank, iv, L.heads, 0, st));
                 mix_cols = L.heads * L.vdim;
-                if (!kIsF32) {
-                    cast_kernel<T><<<cast_grid((size_t)Tn * mix_cols), 256, 0, st>>>(oraw, mix, (size_t)Tn * mix_cols);
-                    m->launches++;
-                } else {
-                    mix_in = reinterpret_cast<const T*>(oraw);
-                }
+                mix_in = expanded;
             }
         } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
             GlaArgs A;
@@ -1909,7 +1922,10 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         CU(linear<T>(m, mix_in, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));
         const bool last = n + 1 == m->runs.size();
         const float* next_norm1 = last ? nullptr : m->layers[m->runs[n + 1].layer].norm1;
-        // the feed-forward reads hn and leaves its output in y
+        // the feed-forward reads hn and leaves its output in y (routed experts under the post-norm block: in `routed`)
+        RoutedSum routed;
+        routed.yp = nullptr; routed.slot_of = nullptr; routed.sel_w = nullptr; routed.top = 0;
+        const RoutedSum no_sum = routed;
         auto feed_forward = [&]() -> int {
             if (L.mlp == SMOL_LM_MLP_POLYNORM) {
                 CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
@@ -1958,13 +1974,16 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                     io2.tile_group = tile_g; io2.tile_row0 = tile_r; io2.seg = seg; io2.n_tiles = n_tiles;
                     const size_t act_n = (size_t)pairs * L.ff;
                     if (few) {
-                        const bf16* hb = reinterpret_cast<const bf16*>(hn);
-                        moe_gemv_kernel<<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(hb, perm, L.top_k, sel_id, seg + L.n_experts,
-                                                                                         reinterpret_cast<const bf16*>(L.w_experts_in), io.sw, zp, 2 * L.ff, D);
-                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
-                        moe_gemv_kernel<<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(reinterpret_cast<const bf16*>(actp), perm, 0, sel_id, seg + L.n_experts,
-                                                                                   reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
-                        m->launches += 2;
+                        moe_gemv_kernel<-1><<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(hn, perm, L.top_k, sel_id, seg + L.n_experts,
+                                                                                            reinterpret_cast<const bf16*>(L.w_experts_in), io.sw, zp, 2 * L.ff, D);
+                        // the second product applies the activation as it reads the first one's result
+                        if (L.mlp_act == SMOL_LM_ACT_SILU)
+                            moe_gemv_kernel<SMOL_LM_ACT_SILU><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
+                                                                                                        reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
+                        else
+                            moe_gemv_kernel<SMOL_LM_ACT_GELU_TANH><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
+                                                                                                             reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
+                        m->launches += 1;
                     } else {
                         bool done = false;
                         if (big) {
@@ -1986,9 +2005,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 } else {
                     CU(cudaMemsetAsync(slot_of, 0xff, (size_t)pairs * 4, st));
                 }
-                if (postnorm) moe_combine_kernel<float><<<Tn, nthr, 0, st>>>(x, yp, slot_of, sel_w, L.top_k, D, y);
-                else moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, sel_w, L.top_k, D, y);
-                m->launches += 1;
+                if (postnorm) {
+                    routed.yp = yp; routed.slot_of = slot_of; routed.sel_w = sel_w; routed.top = L.top_k;      // summed by the norm that follows
+                } else {
+                    moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, sel_w, L.top_k, D, y);
+                    m->launches += 1;
+                }
             }
             return SMOL_OK;
         };
@@ -1997,13 +2019,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             // and the stream becomes the weighted sum of the history
             const bool has_ff = L.mlp != SMOL_LM_MLP_NONE;
             post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm1, c.norm_eps, D, has_ff ? nullptr : hist,
-                                                                      hist_stride, (int)n + 2, L.depth_mix, nullptr, hn);
+                                                                      hist_stride, (int)n + 2, L.depth_mix, nullptr, hn, no_sum);
             m->launches += 1;
             if (has_ff) {
                 const int rc = feed_forward();
                 if (rc != SMOL_OK) return rc;
                 post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm2, c.norm_eps, D, hist, hist_stride,
-                                                                          (int)n + 2, L.depth_mix, nullptr, hn);
+                                                                          (int)n + 2, L.depth_mix, nullptr, hn, routed);
                 m->launches += 1;
             }
         } else if (L.mlp != SMOL_LM_MLP_NONE) {
@@ -2019,12 +2041,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (s->n_want > 0) {
-        if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, D * sizeof(float), st>>>(x, nullptr, 1.0f, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
-                                                                                      nullptr, s->want_rows, hw);
+        if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, D * sizeof(float), st>>>(x, nullptr, c.logit_scale, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
+                                                                                      nullptr, s->want_rows, hw, RoutedSum{nullptr, nullptr, nullptr, 0});
         else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
         m->launches++;
         CU(linear<T>(m, hw, static_cast<const T*>(m->g.head), s->logits, s->n_want, c.vocab, D, st));
-        if (c.logit_scale != 1.0f) {
+        if (!postnorm && c.logit_scale != 1.0f) {
             scale_kernel<<<cast_grid((size_t)s->n_want * c.vocab), 256, 0, st>>>(s->logits, c.logit_scale, (size_t)s->n_want * c.vocab);
             m->launches++;
         }

@@ -48,24 +48,44 @@ __global__ void embed_gain_norm_kernel(const int32_t* __restrict__ tokens, const
 // x <- g * rms_divide(alpha * x + y).  Inside a layer (hist == nullptr) that is the next sublayer's input.  At the end of
 // a layer the row is the layer's result: it is stored as history entry n_hist - 1, and the stream becomes
 // sum_j mix[j] * history[j] over the n_hist entries (entry 0: the embedding output), summed in ascending j.
-// `rows` selects rows (final norm of the wanted rows): then only hn is written, alpha = 1 and y is not read.
+// `rows` selects rows (final norm of the wanted rows): then only hn is written, y is not read, and alpha multiplies the
+// result instead (the scale of the logits, applied before the head's product).
+// The sublayer's output of a routed feed-forward, summed on the fly: for the `top` choices k of a token (ascending),
+// weight[k] * (row slot_of[k] of the experts' outputs, or the token's input itself where slot_of[k] < 0: an identity output).
+struct RoutedSum {
+    const float* yp;              // nullptr: the sublayer's output is y
+    const int32_t* slot_of;
+    const float* sel_w;
+    int top;
+};
+
 template <class T>
 __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ gain, float eps,
                                  int D, float* __restrict__ hist, size_t hist_stride, int n_hist, const float* __restrict__ mix,
-                                 const int32_t* __restrict__ rows, T* __restrict__ hn) {
+                                 const int32_t* __restrict__ rows, T* __restrict__ hn, const RoutedSum rs) {
     extern __shared__ float row[];
     __shared__ float red[33];
     const size_t o = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * D, oo = (size_t)blockIdx.x * D;
     float ss = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float v = rows ? x[o + c] : fmaf(alpha, x[o + c], y[o + c]);
+        float v = x[o + c];
+        if (rs.yp) {
+            float acc = 0.0f;
+            for (int k = 0; k < rs.top; ++k) {
+                const int slot = rs.slot_of[(size_t)blockIdx.x * rs.top + k];
+                acc = fmaf(rs.sel_w[(size_t)blockIdx.x * rs.top + k], slot >= 0 ? rs.yp[(size_t)slot * D + c] : v, acc);
+            }
+            v = fmaf(alpha, v, acc);
+        } else if (!rows) {
+            v = fmaf(alpha, v, y[o + c]);
+        }
         row[c] = v;
         ss += v * v;
     }
     ss = block_sum(ss, red);
     const float r = gain[0] / sqrtf(ss / (float)D + eps);
     if (rows) {
-        for (int c = threadIdx.x; c < D; c += blockDim.x) hn[oo + c] = from_f<T>(row[c] * r);
+        for (int c = threadIdx.x; c < D; c += blockDim.x) hn[oo + c] = from_f<T>(row[c] * r * alpha);
         return;
     }
     if (!hist) {
@@ -87,12 +107,6 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
     }
 }
 
-// fp32 -> T, n elements (an fp32 matrix-product result that feeds the next product)
-template <class T>
-__global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = from_f<T>(src[i]);
-}
-
 __global__ void scale_kernel(float* __restrict__ v, float scale, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) v[i] *= scale;
 }
@@ -105,9 +119,9 @@ __global__ void scale_kernel(float* __restrict__ v, float scale, size_t n) {
 // expanding every cached latent into per-head keys and values, without ever doing so.
 struct LatentArgs {
     const float* proj;
-    int n_in, q_rank, kv_rank, rot, H, d;
+    int n_in, q_rank, kv_rank, rot, rot_pairs, H, d;  // rot_pairs: leading pairs of the rotated part that are rotated
     float eps;
-    const float *q_lat_norm, *kv_lat_norm, *freq;     // freq [rot / 2]: base^(-2i / rot)
+    const float *q_lat_norm, *kv_lat_norm, *freq;     // freq [rot_pairs]: base^(-i / rot_pairs)
     const int32_t *tok_seq, *tok_pos, *block_table;
     int max_pages, page_size, n_pages, n_tokens;
     size_t page_elems, k_off;
@@ -147,33 +161,34 @@ __global__ void latent_prep_kernel(const LatentArgs A, T* __restrict__ cq, T* __
     ss = block_sum(ss, red);
     const float rk = 1.0f / sqrtf(ss / (float)A.kv_rank + A.eps);
     for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) dst[c] = from_f<T>(kv[c] * rk * A.kv_lat_norm[c]);
-    for (int i = threadIdx.x; i < A.rot / 2; i += blockDim.x) {
+    for (int i = threadIdx.x; i < A.rot_pairs; i += blockDim.x) {
         float ra, rb;
         rotate_pair(kv[A.kv_rank + 2 * i], kv[A.kv_rank + 2 * i + 1], pos, A.freq[i], ra, rb);
         dst[A.kv_rank + 2 * i] = from_f<T>(ra);
         dst[A.kv_rank + 2 * i + 1] = from_f<T>(rb);
     }
+    for (int c = 2 * A.rot_pairs + threadIdx.x; c < A.rot; c += blockDim.x) dst[A.kv_rank + c] = from_f<T>(kv[A.kv_rank + c]);
 }
 
-// The attention query of (token, head): qlat (fp32 [T][H][kv_rank], the unrotated query carried into the latent space)
-// followed by the rotated part of q (fp32 [T][H][d + rot]).  One warp per (token, head).
+// The rotated part of the attention query of (token, head): the last rot coordinates of q's head (fp32 [T][H][d + rot]),
+// rotated, behind the query's latent-space part in qbuf ([T][H][kv_rank + rot], which the per-head product has written).
+// One warp per (token, head).
 template <class T>
-__global__ void latent_query_kernel(const LatentArgs A, const float* __restrict__ q, const float* __restrict__ qlat, T* __restrict__ qbuf) {
+__global__ void latent_query_kernel(const LatentArgs A, const float* __restrict__ q, T* __restrict__ qbuf) {
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= A.n_tokens * A.H) return;
     const int t = unit / A.H;
     const int pos = A.tok_pos[t];
     T* dst = qbuf + (size_t)unit * (A.kv_rank + A.rot);
-    const float* src = qlat + (size_t)unit * A.kv_rank;
-    for (int c = lane; c < A.kv_rank; c += 32) dst[c] = from_f<T>(src[c]);
     const float* qr = q + (size_t)unit * (A.d + A.rot) + A.d;
-    for (int i = lane; i < A.rot / 2; i += 32) {
+    for (int i = lane; i < A.rot_pairs; i += 32) {
         float ra, rb;
         rotate_pair(qr[2 * i], qr[2 * i + 1], pos, A.freq[i], ra, rb);
         dst[A.kv_rank + 2 * i] = from_f<T>(ra);
         dst[A.kv_rank + 2 * i + 1] = from_f<T>(rb);
     }
+    for (int c = 2 * A.rot_pairs + lane; c < A.rot; c += 32) dst[A.kv_rank + c] = from_f<T>(qr[c]);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -508,8 +523,11 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int32_t* __r
 // The grouped product for a handful of rows (decoding): one warp per (sorted row, output column), lanes cut K into 16-byte
 // pieces, the expert's weight row is streamed once.  Sorted row r belongs to pair perm[r], whose router output names the
 // expert; it reads a's row perm[r] / gather_div (gather_div == 0: row r itself).  Needs K % 8 == 0 and 16-byte aligned rows.
+// ACT >= 0: a is instead the fp32 result of the first product [rows][2 K] (gate | up), and the row is act(gate) * up, rounded
+// to bf16 as the tile forms round it.
 constexpr int kMoeGemvPairs = 32;
-__global__ void __launch_bounds__(256) moe_gemv_kernel(const bf16* __restrict__ a, const int32_t* __restrict__ perm, int gather_div,
+template <int ACT>
+__global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ a_any, const int32_t* __restrict__ perm, int gather_div,
                                                        const int32_t* __restrict__ sel_id, const int32_t* __restrict__ n_sorted,
                                                        const bf16* __restrict__ w, long long w_stride, float* __restrict__ y, int N, int K) {
     const int r = blockIdx.y;
@@ -518,8 +536,23 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const bf16* __restrict__ 
     if (n >= N) return;
     const int pair = perm[r];
     const bf16* wr = w + (long long)sel_id[pair] * w_stride + (size_t)n * K;
-    const bf16* ar = a + (size_t)(gather_div > 0 ? pair / gather_div : r) * K;
     float acc = 0.0f;
+    if (ACT >= 0) {
+        const float* zr = static_cast<const float*>(a_any) + (size_t)r * 2 * K;
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 wv = ldg_stream(wr + k);
+            const float4 g0 = *reinterpret_cast<const float4*>(zr + k), g1 = *reinterpret_cast<const float4*>(zr + k + 4);
+            const float4 u0 = *reinterpret_cast<const float4*>(zr + K + k), u1 = *reinterpret_cast<const float4*>(zr + K + k + 4);
+            acc = fmaf(bf16_round(gated_act_(ACT, g0.x) * u0.x), bf_lo(wv.x), acc); acc = fmaf(bf16_round(gated_act_(ACT, g0.y) * u0.y), bf_hi(wv.x), acc);
+            acc = fmaf(bf16_round(gated_act_(ACT, g0.z) * u0.z), bf_lo(wv.y), acc); acc = fmaf(bf16_round(gated_act_(ACT, g0.w) * u0.w), bf_hi(wv.y), acc);
+            acc = fmaf(bf16_round(gated_act_(ACT, g1.x) * u1.x), bf_lo(wv.z), acc); acc = fmaf(bf16_round(gated_act_(ACT, g1.y) * u1.y), bf_hi(wv.z), acc);
+            acc = fmaf(bf16_round(gated_act_(ACT, g1.z) * u1.z), bf_lo(wv.w), acc); acc = fmaf(bf16_round(gated_act_(ACT, g1.w) * u1.w), bf_hi(wv.w), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[(size_t)r * N + n] = acc;
+        return;
+    }
+    const bf16* ar = static_cast<const bf16*>(a_any) + (size_t)(gather_div > 0 ? pair / gather_div : r) * K;
     for (int k = lane * 8; k < K; k += 256) {
         const uint4 wv = ldg_stream(wr + k), av = ldg_v4(ar + k);
         acc = fmaf(bf_lo(av.x), bf_lo(wv.x), acc); acc = fmaf(bf_hi(av.x), bf_hi(wv.x), acc);

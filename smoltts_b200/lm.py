@@ -381,7 +381,7 @@ class MaferaxLM(HybridLM):
             c.depth_mix = vec(p + "dwa").data_ptr()
             if m.kind == "latent_attention":
                 c.kv_heads, c.rank = 1, 0
-                c.rot_dim, c.q_rank, c.kv_rank, c.rot_base, c.score_scale = m.rot_dim, m.q_rank, m.kv_rank, m.rot_base, m.scale
+                c.rot_dim, c.rot_dims, c.q_rank, c.kv_rank, c.rot_base, c.score_scale = m.rot_dim, m.rot_dims, m.q_rank, m.kv_rank, m.rot_base, m.scale
                 c.w_in = mat(p + "mix.dq", p + "mix.dkv", p + "mix.g").data_ptr()
                 c.w_q_up = mat(p + "mix.uq").data_ptr()
                 # the key expansion of every head, transposed: [heads][kv_rank][dim] (exact: a change of layout only)

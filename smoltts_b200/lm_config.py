@@ -179,15 +179,15 @@ class LatentAttentionSpec:
     kv_rank: int
     scale: float
     rot_base: float
-    rot_dims: int         # coordinates the rotation acts on (here: all rot_dim)
+    rot_dims: int         # leading coordinates of the rotated part the rotation acts on (the design: all rot_dim)
 
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "LatentAttentionSpec":
         rot = d["rot"]
         spec = cls(int(d["heads"]), int(d["dim"]), int(d["rot_dim"]), int(d["vdim"]), int(d["q_rank"]), int(d["kv_rank"]),
                    float(d["scale"]), float(rot["base"]), int(rot.get("dims", d["rot_dim"])))
-        if spec.rot_dims != spec.rot_dim or spec.rot_dim % 2:
-            raise ValueError("latent attention rotates its whole rotated part: rot.dims must equal rot_dim, and be even")
+        if spec.rot_dims > spec.rot_dim or spec.rot_dims % 2:
+            raise ValueError("latent attention: rot.dims must be even and at most rot_dim")
         return spec
 
     def to_dict(self) -> Dict[str, Any]:

@@ -15,10 +15,10 @@ def moe(experts=6, identity=2, top=2, groups=4, keep=2, scale=1.5, ff=24):
             "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}, "scale": scale}}
 
 
-def latent(heads=4, dim=16, rot_dim=8, vdim=12, q_rank=24, kv_rank=40, scale=0.2, base=5000.0, mlp=None):
+def latent(heads=4, dim=16, rot_dim=8, vdim=12, q_rank=24, kv_rank=40, scale=0.2, base=5000.0, mlp=None, rot_dims=None):
     return {"type": "latent_attention", "mlp": mlp,
             "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale,
-                      "rot": {"base": base, "dims": rot_dim}}}
+                      "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims}}}
 
 
 def gla(heads=2, dim=16, vdim=24, tau=8.0, rank=8, mlp=None):

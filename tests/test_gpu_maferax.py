@@ -41,6 +41,7 @@ LAYERS = {
     "latent-rank260": [latent(heads=2, dim=24, rot_dim=12, vdim=16, q_rank=16, kv_rank=260, scale=0.1)],
     "latent-12heads": [latent(heads=12, dim=8, rot_dim=8, vdim=8, q_rank=32, kv_rank=32, scale=0.25)],
     "latent-norot": [latent(heads=2, dim=16, rot_dim=0, vdim=16, q_rank=16, kv_rank=32)],
+    "latent-part-rotated": [latent(heads=2, dim=8, rot_dim=12, rot_dims=8, vdim=8, q_rank=16, kv_rank=20, scale=0.3, base=30.0)],
     "gla": [gla()],
     "gla-1head-32": [gla(heads=1, dim=32, vdim=8, rank=3)],
     "gla-odd": [gla(heads=2, dim=6, vdim=10, tau=1.0, rank=7)],
@@ -96,6 +97,22 @@ def test_every_layer_of_a_hybrid_and_the_depth_average(dtype):
         assert rel_err(MaferaxOracle(MIXED, w2).forward(toks), want) > 30 * TOL[F32]
         other = dict(MIXED, postln_alpha=1.0)
         assert rel_err(MaferaxOracle(other, w).forward(toks), want) > 30 * TOL[F32]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_odd_width_and_vocabulary(dtype):
+    """Sizes that are multiples of nothing: no 16-byte pieces anywhere, every kernel on its element-wise form."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([gla(heads=1, dim=10, vdim=6, rank=3, mlp=moe(experts=3, identity=0, top=2, groups=1, keep=1, ff=9)),
+                  latent(heads=3, dim=6, rot_dim=2, vdim=5, q_rank=7, kv_rank=9, mlp=dense(11))], vocab=37, width=50)
+    model, orc, _ = engine_and_oracle(cfg, seed=14, dtype=dtype)
+    toks = tokens(45, 37, 41)
+    want = orc.forward(toks)
+    b = TokenBatcher(model)
+    got = torch.cat([b.feed([("w", toks[:30], list(range(30)))])] + [b.feed([("w", [t], [0])]) for t in toks[30:]])
+    b.close()
+    assert rel_err(got, want) < TOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])

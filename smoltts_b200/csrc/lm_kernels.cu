@@ -1382,7 +1382,7 @@ struct SmolLm {
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
     size_t o_hist = 0, o_cq = 0, o_qf = 0, o_freq = 0;
     size_t o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
-    int max_cq = 0, max_qf = 0, max_qlat = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
+    int max_cq = 0, max_qf = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
     int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
     char* ws = nullptr;
@@ -1467,7 +1467,6 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_hd = std::max(m->max_hd, L.heads * L.vdim);
             m->max_cq = std::max(m->max_cq, L.q_rank);
             m->max_qf = std::max(m->max_qf, L.heads * (L.dim + L.rot_dim));
-            m->max_qlat = std::max(m->max_qlat, L.heads * L.kv_rank);
         } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
             if (L.dim > 256) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256"); }
             if (L.rank < 1 || L.vdim < 1 || !(L.decay_tau > 0.0f)) { delete m; return fail(SMOL_ERR_INVALID, "gated linear: rank, vdim, tau must be positive"); }
@@ -1601,6 +1600,12 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
     m->slots = static_cast<float*>(d_slots);
     m->n_pages = n_pages;
     m->n_slots = n_slots;
+    if (m->cfg.block == SMOL_LM_BLOCK_POSTNORM && (size_t)m->cfg.width * 8 > 48 * 1024) {
+        // the post-norm kernel keeps two fp32 copies of a row in shared memory
+        if ((size_t)m->cfg.width * 8 > 200 * 1024) return fail(SMOL_ERR_UNSUPPORTED, "smol_lm_bind: width above 25600 with the post-norm block");
+        CU(cudaFuncSetAttribute(post_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 8));
+        CU(cudaFuncSetAttribute(post_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 8));
+    }
     if (!m->freq_table.empty())
         CU(cudaMemcpy(m->ws + m->o_freq, m->freq_table.data(), m->freq_table.size() * sizeof(float), cudaMemcpyHostToDevice));
     if (m->cfg.block == SMOL_LM_BLOCK_POSTNORM && !g->embed_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: the post-norm block needs embed_norm");
@@ -2018,13 +2023,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             // x <- g1 * rms_divide(alpha x + mixer); x <- g2 * rms_divide(alpha x + ff); the layer's result joins the history
             // and the stream becomes the weighted sum of the history
             const bool has_ff = L.mlp != SMOL_LM_MLP_NONE;
-            post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm1, c.norm_eps, D, has_ff ? nullptr : hist,
+            post_norm_kernel<T><<<Tn, nthr, 2 * D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm1, c.norm_eps, D, has_ff ? nullptr : hist,
                                                                       hist_stride, (int)n + 2, L.depth_mix, nullptr, hn, no_sum);
             m->launches += 1;
             if (has_ff) {
                 const int rc = feed_forward();
                 if (rc != SMOL_OK) return rc;
-                post_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm2, c.norm_eps, D, hist, hist_stride,
+                post_norm_kernel<T><<<Tn, nthr, 2 * D * sizeof(float), st>>>(x, y, c.residual_alpha, L.norm2, c.norm_eps, D, hist, hist_stride,
                                                                           (int)n + 2, L.depth_mix, nullptr, hn, routed);
                 m->launches += 1;
             }
@@ -2041,7 +2046,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (s->n_want > 0) {
-        if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, D * sizeof(float), st>>>(x, nullptr, c.logit_scale, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
+        if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, 2 * D * sizeof(float), st>>>(x, nullptr, c.logit_scale, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
                                                                                       nullptr, s->want_rows, hw, RoutedSum{nullptr, nullptr, nullptr, 0});
         else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
         m->launches++;

@@ -63,11 +63,20 @@ template <class T>
 __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ gain, float eps,
                                  int D, float* __restrict__ hist, size_t hist_stride, int n_hist, const float* __restrict__ mix,
                                  const int32_t* __restrict__ rows, T* __restrict__ hn, const RoutedSum rs) {
-    extern __shared__ float row[];
+    extern __shared__ float row[];          // the row before the division [D], then the earlier history's weighted sum [D]
     __shared__ float red[33];
     const size_t o = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * D, oo = (size_t)blockIdx.x * D;
+    const float* __restrict__ past = hist;   // entries 0 .. n_hist - 2 are only read here, entry n_hist - 1 only written
+    float* pre = row + D;
     float ss = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        if (hist && !rows) {
+            // the earlier layers' share of the new stream does not depend on this row's norm: its loads go out first
+            float acc = 0.0f;
+#pragma unroll 4
+            for (int j = 0; j + 1 < n_hist; ++j) acc = fmaf(mix[j], past[(size_t)j * hist_stride + o + c], acc);
+            pre[c] = acc;
+        }
         float v = x[o + c];
         if (rs.yp) {
             float acc = 0.0f;
@@ -99,9 +108,7 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         const float v = row[c] * r;
         hist[(size_t)(n_hist - 1) * hist_stride + o + c] = v;
-        float acc = 0.0f;
-        for (int j = 0; j + 1 < n_hist; ++j) acc = fmaf(mix[j], hist[(size_t)j * hist_stride + o + c], acc);
-        acc = fmaf(mix[n_hist - 1], v, acc);
+        const float acc = fmaf(mix[n_hist - 1], v, pre[c]);
         x[o + c] = acc;
         hn[o + c] = from_f<T>(acc);
     }
@@ -403,7 +410,18 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
     for (int e = warp; e < A.E; e += nw) {
         const float* wr = A.w_router + (size_t)e * A.D;
         float acc = 0.0f;
-        for (int c = lane; c < A.D; c += 32) acc = fmaf(to_f<TI>(xr[c]), wr[c], acc);
+        if (sizeof(TI) == 4 && A.D % 4 == 0) {          // rows of x and of the router start on 16-byte boundaries
+            const float4* x4 = reinterpret_cast<const float4*>(xr);
+            const float4* w4 = reinterpret_cast<const float4*>(wr);
+#pragma unroll 4
+            for (int c = lane; c < A.D / 4; c += 32) {
+                const float4 a = x4[c], b = w4[c];
+                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+#pragma unroll 4
+            for (int c = lane; c < A.D; c += 32) acc = fmaf(to_f<TI>(xr[c]), wr[c], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) s[e] = acc;
     }

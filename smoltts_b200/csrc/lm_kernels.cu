@@ -1381,8 +1381,8 @@ struct SmolLm {
     // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
     size_t o_hist = 0, o_cq = 0, o_qf = 0, o_freq = 0;
-    size_t o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
-    int max_cq = 0, max_qf = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
+    size_t o_rlogits = 0, o_rdone = 0, o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
+    int max_routed = 0, max_cq = 0, max_qf = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
     int split_len = 256, max_splits = 1, max_heads = 1, max_vdim = 1;
     char* ws = nullptr;
@@ -1492,6 +1492,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
                 return fail(SMOL_ERR_INVALID, "routed feed-forward: experts, groups and top do not fit each other");
             }
             m->max_top = std::max(m->max_top, L.top_k);
+            m->max_routed = std::max(m->max_routed, E);
             m->max_experts = std::max(m->max_experts, L.n_experts);
             m->max_pair_ff = std::max(m->max_pair_ff, L.top_k * L.ff);
         }
@@ -1543,6 +1544,8 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
         m->o_actp = carve(T * (size_t)m->max_pair_ff * E);
         m->o_yp = carve(pairs * D * 4);
         m->o_ap = carve(pairs * D * E);
+        m->o_rlogits = carve(T * (size_t)m->max_routed * 4);
+        m->o_rdone = carve(T * 4);          // counters: zero between steps (the caller's workspace starts zeroed; the kernel resets them)
     }
     m->total = o;
     *out = m;
@@ -1606,6 +1609,7 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
         CU(cudaFuncSetAttribute(post_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 8));
         CU(cudaFuncSetAttribute(post_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 8));
     }
+    if (m->max_top > 0) CU(cudaMemset(m->ws + m->o_rdone, 0, (size_t)m->cfg.max_step_tokens * 4));      // the router's per-token counters
     if (!m->freq_table.empty())
         CU(cudaMemcpy(m->ws + m->o_freq, m->freq_table.data(), m->freq_table.size() * sizeof(float), cudaMemcpyHostToDevice));
     if (m->cfg.block == SMOL_LM_BLOCK_POSTNORM && !g->embed_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: the post-norm block needs embed_norm");
@@ -1959,8 +1963,11 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 Rt.top = L.top_k; Rt.n_groups = L.n_groups; Rt.keep = L.keep_groups; Rt.scale = L.router_scale; Rt.n_tokens = Tn;
                 const int pairs = Tn * L.top_k;
                 // the router reads the sublayer's input in fp32 where the block keeps it (post-norm), else its T form
-                if (postnorm) moe_route_kernel<float><<<Tn, 128, 0, st>>>(Rt, x, sel_id, sel_w);
-                else moe_route_kernel<T><<<Tn, 128, 0, st>>>(Rt, hn, sel_id, sel_w);
+                float* r_logits = reinterpret_cast<float*>(m->ws + m->o_rlogits);
+                int32_t* r_done = reinterpret_cast<int32_t*>(m->ws + m->o_rdone);
+                const dim3 rgrid(Tn, (Rt.E + 3) / 4);
+                if (postnorm) moe_route_kernel<float><<<rgrid, 128, 0, st>>>(Rt, x, r_logits, r_done, sel_id, sel_w);
+                else moe_route_kernel<T><<<rgrid, 128, 0, st>>>(Rt, hn, r_logits, r_done, sel_id, sel_w);
                 m->launches += 1;
                 if (L.n_experts > 0) {
                     // three forms of the two grouped products, by how many rows an expert gets: a warp per output column for

@@ -69,6 +69,15 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
     const float* __restrict__ past = hist;   // entries 0 .. n_hist - 2 are only read here, entry n_hist - 1 only written
     float* pre = row + D;
     float ss = 0.0f;
+    // a routed sublayer: the token's rows and weights are the same for every column (up to 8 kept in registers)
+    int slot_r[8];
+    float wt_r[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const bool in = rs.yp && k < rs.top;
+        slot_r[k] = in ? rs.slot_of[(size_t)blockIdx.x * rs.top + k] : -1;
+        wt_r[k] = in ? rs.sel_w[(size_t)blockIdx.x * rs.top + k] : 0.0f;
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         if (hist && !rows) {
             // the earlier layers' share of the new stream does not depend on this row's norm: its loads go out first
@@ -80,7 +89,10 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
         float v = x[o + c];
         if (rs.yp) {
             float acc = 0.0f;
-            for (int k = 0; k < rs.top; ++k) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < rs.top) acc = fmaf(wt_r[k], slot_r[k] >= 0 ? rs.yp[(size_t)slot_r[k] * D + c] : v, acc);
+            for (int k = 8; k < rs.top; ++k) {
                 const int slot = rs.slot_of[(size_t)blockIdx.x * rs.top + k];
                 acc = fmaf(rs.sel_w[(size_t)blockIdx.x * rs.top + k], slot >= 0 ? rs.yp[(size_t)slot * D + c] : v, acc);
             }
@@ -397,18 +409,24 @@ struct RouteArgs {
 constexpr int kMaxRouted = 1024;       // router outputs (experts + identity outputs)
 constexpr int kMaxTop = 32;
 
-// One block per token: fp32 logits over all router outputs, softmax scores s, choice scores s + bias; outputs outside the
-// `keep` best groups (a group's score: its best choice score) cannot be chosen; the `top` best choice scores are chosen
-// (ties: the lower index), their weights are the scores s over their sum, times `scale`.
+// Blocks (token, group of 4 router outputs): one warp per output takes the fp32 dot product of the token's input and the
+// output's router row and leaves it in `logits`.  The block that finishes a token last (a counter per token, which it
+// sets back to zero) then chooses: softmax scores s, choice scores s + bias; outputs outside the `keep` best groups (a
+// group's score: its best choice score) cannot be chosen; the `top` best choice scores are chosen (ties: the lower
+// index; the choices are kept in that order), their weights are the scores s over their sum, times `scale`.  Ranks are
+// counted, not sorted: output e is chosen if fewer than `top` allowed outputs beat it.
 template <class TI>
-__global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const TI* __restrict__ x, int32_t* __restrict__ sel_id,
-                                                        float* __restrict__ sel_w) {
-    __shared__ float s[kMaxRouted], choice[kMaxRouted];
+__global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const TI* __restrict__ x, float* __restrict__ logits,
+                                                        int32_t* __restrict__ done, int32_t* __restrict__ sel_id, float* __restrict__ sel_w) {
+    __shared__ float s[kMaxRouted], choice[kMaxRouted], gscore[kMaxRouted];
     __shared__ float red[33];
+    __shared__ float top_s[kMaxTop];
+    __shared__ int last;
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const TI* xr = x + (size_t)t * A.D;
-    for (int e = warp; e < A.E; e += nw) {
-        const float* wr = A.w_router + (size_t)e * A.D;
+    const int e0 = blockIdx.y * nw + warp;
+    if (e0 < A.E) {
+        const float* wr = A.w_router + (size_t)e0 * A.D;
         float acc = 0.0f;
         if (sizeof(TI) == 4 && A.D % 4 == 0) {          // rows of x and of the router start on 16-byte boundaries
             const float4* x4 = reinterpret_cast<const float4*>(xr);
@@ -423,11 +441,24 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
             for (int c = lane; c < A.D; c += 32) acc = fmaf(to_f<TI>(xr[c]), wr[c], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
+        if (lane == 0) logits[(size_t)t * A.E + e0] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&done[t], 1);
+        last = ticket == (int)gridDim.y - 1;
+        if (last) done[t] = 0;
     }
     __syncthreads();
+    if (!last) return;
+    __threadfence();
     float mx = -INFINITY;
-    for (int e = threadIdx.x; e < A.E; e += blockDim.x) mx = fmaxf(mx, s[e]);
+    for (int e = threadIdx.x; e < A.E; e += blockDim.x) {
+        const float v = __ldcg(logits + (size_t)t * A.E + e);
+        s[e] = v;
+        mx = fmaxf(mx, v);
+    }
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
     __syncthreads();
@@ -442,41 +473,39 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
         choice[e] = p + A.bias[e];
     }
     __syncthreads();
-    if (threadIdx.x != 0) return;
     const int size = A.E / A.n_groups;
     if (A.keep < A.n_groups) {
-        // drop the n_groups - keep worst groups: repeatedly find the worst group still allowed (ties: the higher index goes)
-        uint32_t dropped[kMaxRouted / 32];
-        for (int i = 0; i < (A.n_groups + 31) / 32; ++i) dropped[i] = 0u;
-        for (int n = 0; n < A.n_groups - A.keep; ++n) {
-            int worst = -1;
-            float ws = 0.0f;
-            for (int g = 0; g < A.n_groups; ++g) {
-                if (dropped[g >> 5] >> (g & 31) & 1u) continue;
-                float gs = -INFINITY;
-                for (int e = g * size; e < (g + 1) * size; ++e) gs = fmaxf(gs, choice[e]);
-                if (worst < 0 || gs <= ws) { worst = g; ws = gs; }
-            }
-            dropped[worst >> 5] |= 1u << (worst & 31);
-            for (int e = worst * size; e < (worst + 1) * size; ++e) choice[e] = -INFINITY;
+        for (int g = threadIdx.x; g < A.n_groups; g += blockDim.x) {
+            float gs = -INFINITY;
+            for (int e = g * size; e < (g + 1) * size; ++e) gs = fmaxf(gs, choice[e]);
+            gscore[g] = gs;
+        }
+        __syncthreads();
+        // a group is kept if fewer than `keep` groups beat it (a higher score, or the same score and a lower index)
+        for (int g = threadIdx.x; g < A.n_groups; g += blockDim.x) {
+            const float gs = gscore[g];
+            int better = 0;
+            for (int h = 0; h < A.n_groups; ++h) better += (gscore[h] > gs || (gscore[h] == gs && h < g)) ? 1 : 0;
+            if (better >= A.keep)
+                for (int e = g * size; e < (g + 1) * size; ++e) choice[e] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    for (int e = threadIdx.x; e < A.E; e += blockDim.x) {
+        const float ce = choice[e];
+        if (ce == -INFINITY) continue;
+        int better = 0;
+        for (int f = 0; f < A.E; ++f) better += (choice[f] > ce || (choice[f] == ce && f < e)) ? 1 : 0;
+        if (better < A.top) {
+            sel_id[(size_t)t * A.top + better] = e;
+            top_s[better] = s[e];
         }
     }
-    int ids[kMaxTop];
-    float den = 0.0f;
-    for (int k = 0; k < A.top; ++k) {
-        int best = -1;
-        float bs = -INFINITY;
-        for (int e = 0; e < A.E; ++e)
-            if (choice[e] > bs) { best = e; bs = choice[e]; }
-        if (best < 0) best = 0;          // fewer allowed outputs than `top`: not a configuration the engine accepts
-        ids[k] = best;
-        choice[best] = -INFINITY;
-        den += s[best];
-    }
-    den += 1e-20f;
-    for (int k = 0; k < A.top; ++k) {
-        sel_id[(size_t)t * A.top + k] = ids[k];
-        sel_w[(size_t)t * A.top + k] = s[ids[k]] / den * A.scale;
+    __syncthreads();
+    if (threadIdx.x < A.top) {
+        float den = 0.0f;
+        for (int k = 0; k < A.top; ++k) den += top_s[k];
+        sel_w[(size_t)t * A.top + threadIdx.x] = top_s[threadIdx.x] / (den + 1e-20f) * A.scale;
     }
 }
 

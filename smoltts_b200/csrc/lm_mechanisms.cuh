@@ -78,6 +78,73 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
         slot_r[k] = in ? rs.slot_of[(size_t)blockIdx.x * rs.top + k] : -1;
         wt_r[k] = in ? rs.sel_w[(size_t)blockIdx.x * rs.top + k] : 0.0f;
     }
+    if (D <= (int)blockDim.x * kRowRegs) {
+        // the row in registers: every load of a stage is issued before the first use, so a lone row (decoding) waits for
+        // global memory a few times, not once per element
+        float v[kRowRegs], pre_r[kRowRegs];
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            v[i] = c < D ? x[o + c] : 0.0f;
+            pre_r[i] = 0.0f;
+        }
+        if (rs.yp) {
+            float acc[kRowRegs];
+#pragma unroll
+            for (int i = 0; i < kRowRegs; ++i) acc[i] = 0.0f;
+            for (int k = 0; k < rs.top; ++k) {
+                const int slot = k < 8 ? slot_r[k] : rs.slot_of[(size_t)blockIdx.x * rs.top + k];
+                const float wk = k < 8 ? wt_r[k] : rs.sel_w[(size_t)blockIdx.x * rs.top + k];
+#pragma unroll
+                for (int i = 0; i < kRowRegs; ++i) {
+                    const int c = threadIdx.x + i * blockDim.x;
+                    if (c < D) acc[i] = fmaf(wk, slot >= 0 ? rs.yp[(size_t)slot * D + c] : v[i], acc[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kRowRegs; ++i) v[i] = fmaf(alpha, v[i], acc[i]);
+        } else if (!rows) {
+#pragma unroll
+            for (int i = 0; i < kRowRegs; ++i) {
+                const int c = threadIdx.x + i * blockDim.x;
+                if (c < D) v[i] = fmaf(alpha, v[i], y[o + c]);
+            }
+        }
+        if (hist && !rows) {
+#pragma unroll 2
+            for (int j = 0; j + 1 < n_hist; ++j) {
+                const float mj = mix[j];
+#pragma unroll
+                for (int i = 0; i < kRowRegs; ++i) {
+                    const int c = threadIdx.x + i * blockDim.x;
+                    if (c < D) pre_r[i] = fmaf(mj, past[(size_t)j * hist_stride + o + c], pre_r[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) ss += v[i] * v[i];
+        ss = block_sum(ss, red);
+        const float r = gain[0] / sqrtf(ss / (float)D + eps);
+        const float m_last = (hist && !rows) ? mix[n_hist - 1] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c >= D) continue;
+            const float w = v[i] * r;
+            if (rows) {
+                hn[oo + c] = from_f<T>(w * alpha);
+            } else if (!hist) {
+                x[o + c] = w;
+                hn[o + c] = from_f<T>(w);
+            } else {
+                hist[(size_t)(n_hist - 1) * hist_stride + o + c] = w;
+                const float acc = fmaf(m_last, w, pre_r[i]);
+                x[o + c] = acc;
+                hn[o + c] = from_f<T>(acc);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         if (hist && !rows) {
             // the earlier layers' share of the new stream does not depend on this row's norm: its loads go out first
@@ -158,27 +225,33 @@ __device__ __forceinline__ void rotate_pair(float a, float b, int pos, float fre
 // One block per token: the normed query latent -> cq (T), the normed key/value latent and the rotated key part -> the pool.
 template <class T>
 __global__ void latent_prep_kernel(const LatentArgs A, T* __restrict__ cq, T* __restrict__ pool) {
-    __shared__ float red[33];
+    __shared__ float red[2][33];
     const int t = blockIdx.x;
     const float* row = A.proj + (size_t)t * A.n_in;
-    float ss = 0.0f;
-    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) ss += row[c] * row[c];
-    ss = block_sum(ss, red);
-    const float rq = 1.0f / sqrtf(ss / (float)A.q_rank + A.eps);
-    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) cq[(size_t)t * A.q_rank + c] = from_f<T>(row[c] * rq * A.q_lat_norm[c]);
+    const float* kv = row + A.q_rank;
+    // the page lookup and both sums of squares start together: their loads do not wait for one another
     const int pos = A.tok_pos[t];
     const int pg = pos / A.page_size, in_pg = pos % A.page_size;
     const int page = pg < A.max_pages ? A.block_table[(size_t)A.tok_seq[t] * A.max_pages + pg] : -1;
+    float sq = 0.0f, sk = 0.0f;
+    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) sq += row[c] * row[c];
+    for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) sk += kv[c] * kv[c];
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) { red[0][w] = sq; red[1][w] = sk; }
+    __syncthreads();
+    sq = 0.0f;
+    sk = 0.0f;
+    for (int i = 0; i < nw; ++i) { sq += red[0][i]; sk += red[1][i]; }      // the same order in every thread
+    const float rq = 1.0f / sqrtf(sq / (float)A.q_rank + A.eps);
+    for (int c = threadIdx.x; c < A.q_rank; c += blockDim.x) cq[(size_t)t * A.q_rank + c] = from_f<T>(row[c] * rq * A.q_lat_norm[c]);
     if (page < 0 || page >= A.n_pages) {
         if (threadIdx.x == 0) atomicExch(A.err, 1);
         return;
     }
     T* dst = pool + (size_t)page * A.page_elems + A.k_off + (size_t)in_pg * (A.kv_rank + A.rot);
-    const float* kv = row + A.q_rank;
-    ss = 0.0f;
-    for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) ss += kv[c] * kv[c];
-    ss = block_sum(ss, red);
-    const float rk = 1.0f / sqrtf(ss / (float)A.kv_rank + A.eps);
+    const float rk = 1.0f / sqrtf(sk / (float)A.kv_rank + A.eps);
     for (int c = threadIdx.x; c < A.kv_rank; c += blockDim.x) dst[c] = from_f<T>(kv[c] * rk * A.kv_lat_norm[c]);
     for (int i = threadIdx.x; i < A.rot_pairs; i += blockDim.x) {
         float ra, rb;

@@ -80,7 +80,9 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
     }
     if (D <= (int)blockDim.x * kRowRegs) {
         // the row in registers: every load of a stage is issued before the first use, so a lone row (decoding) waits for
-        // global memory a few times, not once per element
+        // global memory a few times, not once per element; the gain and the row's own weight are read before the reduction
+        const float g0 = gain[0];
+        const float m_last = (hist && !rows) ? mix[n_hist - 1] : 0.0f;
         float v[kRowRegs], pre_r[kRowRegs];
 #pragma unroll
         for (int i = 0; i < kRowRegs; ++i) {
@@ -124,8 +126,7 @@ __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict_
 #pragma unroll
         for (int i = 0; i < kRowRegs; ++i) ss += v[i] * v[i];
         ss = block_sum(ss, red);
-        const float r = gain[0] / sqrtf(ss / (float)D + eps);
-        const float m_last = (hist && !rows) ? mix[n_hist - 1] : 0.0f;
+        const float r = g0 / sqrtf(ss / (float)D + eps);
 #pragma unroll
         for (int i = 0; i < kRowRegs; ++i) {
             const int c = threadIdx.x + i * blockDim.x;

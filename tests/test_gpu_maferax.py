@@ -97,6 +97,12 @@ def test_every_layer_of_a_hybrid_and_the_depth_average(dtype):
         assert rel_err(MaferaxOracle(MIXED, w2).forward(toks), want) > 30 * TOL[F32]
         other = dict(MIXED, postln_alpha=1.0)
         assert rel_err(MaferaxOracle(other, w).forward(toks), want) > 30 * TOL[F32]
+        slow = copy.deepcopy(MIXED)
+        slow["layers"][0]["mixer"]["tau"] = 2.0 * MIXED["layers"][0]["mixer"]["tau"]      # ... and the decay's exponent
+        assert rel_err(MaferaxOracle(slow, w).forward(toks), want) > 30 * TOL[F32]
+        w3 = copy.deepcopy(w)
+        w3["l1.mix.g"] = torch.zeros_like(w["l1.mix.g"])                                  # ... and the per-head output gate
+        assert rel_err(MaferaxOracle(MIXED, w3).forward(toks), want) > 30 * TOL[F32]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
